@@ -51,6 +51,15 @@ def _gizulorn(c: dict):
 register_architecture("Gizulorn", _gizulorn)
 
 
+def _nepudra(c: dict):
+    from .nepudra import NepudraConfig
+    cfg = NepudraConfig.from_json(c)
+    return cfg, cfg.spec()
+
+
+register_architecture("Nepudra", _nepudra)
+
+
 def read_config_json(model_dir: str) -> dict:
     path = os.path.join(model_dir, "config.json")
     if not os.path.isfile(path):

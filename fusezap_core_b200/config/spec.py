@@ -67,6 +67,9 @@ class ModelSpec:
     embed_scale: float | None = None          # embeddings are multiplied by this (in float32) as they are gathered
     logit_transform: PartSpec | None = None   # a part (kind in the logit-transform registry) applied to the float32
                                               # logits of the wanted rows, in place, before anything reads them
+    embed_extras: tuple = ()                  # parts (kinds in the embedding-extra registry) that add to the gathered
+                                              # embeddings before the first layer; they name their tensors in full and
+                                              # may keep request state
 
     def validate(self) -> None:
         if self.hidden_size <= 0 or self.vocab_size <= 0:

@@ -12,7 +12,7 @@ import torch
 
 from ..cache import KVNeed
 from ..config import ModelSpec, describe, read_config_json
-from ..parts import BLOCKS, FEED_FORWARDS, LOGIT_TRANSFORMS, MIXERS, NORMS, POSITIONS, build
+from ..parts import BLOCKS, EMBED_EXTRAS, FEED_FORWARDS, LOGIT_TRANSFORMS, MIXERS, NORMS, POSITIONS, build
 from ..weights import ParamSpec, load_weights
 from ..weights.loader import TORCH_DTYPE
 
@@ -43,6 +43,8 @@ def declared_tensors(spec: ModelSpec, layers: list[Any] | None = None) -> dict[s
     """Every tensor name the model reads, in a fixed order, with its shape. Optional groups get the layer's prefix."""
     layers = layers if layers is not None else build_layers(spec)
     out: dict[str, ParamSpec] = {spec.embed_name: ParamSpec((spec.vocab_size, spec.hidden_size))}
+    for ps in spec.embed_extras:
+        out.update(build(EMBED_EXTRAS, "embedding extra", ps).tensors())
     for ls, block in zip(spec.layers, layers):
         for k, p in block.tensors().items():
             out[ls.prefix + k] = replace(p, group=ls.prefix + p.group) if p.group else p
@@ -78,6 +80,7 @@ class DecoderModel:
         self.logit_transform = (build(LOGIT_TRANSFORMS, "logit transform", spec.logit_transform)
                                 if spec.logit_transform is not None else None)
         self.embed_scale = 1.0 if spec.embed_scale is None else float(spec.embed_scale)
+        self.embed_extras = [build(EMBED_EXTRAS, "embedding extra", ps) for ps in spec.embed_extras]
         for n, e in enumerate(spec.schedule):
             pn = self.layers[e.layer].mixer.position_name()
             if pn is not None and pn not in self.positions:
@@ -101,9 +104,13 @@ class DecoderModel:
         return needs
 
     def state_needs(self) -> dict[tuple[int, str], Any]:
-        """(schedule entry, name) -> what the mixer declares: a shape (float32), or (shape, torch dtype)."""
-        return {(n, name): need for n, e in enumerate(self.spec.schedule)
-                for name, need in _state_need(self.layers[e.layer]).items()}
+        """(schedule entry, name) -> what the mixer declares: a shape (float32), or (shape, torch dtype). The state of
+        the embedding's extras, which belong to no layer, stands under entry -1."""
+        out = {(n, name): need for n, e in enumerate(self.spec.schedule)
+               for name, need in _state_need(self.layers[e.layer]).items()}
+        for part in self.embed_extras:
+            out.update({(-1, name): need for name, need in part.state_need().items()})
+        return out
 
     def graph_safe(self) -> bool:
         """True if every part's forward is a fixed sequence of kernels over device data (see `Part.graph_safe`)."""
@@ -112,7 +119,7 @@ class DecoderModel:
     def parts(self) -> list[Any]:
         """Every part of the model, blocks and what they hold included, each once."""
         out, seen = [], set()
-        stack = [self.final_norm, *self.positions.values(), *self.layers]
+        stack = [self.final_norm, *self.positions.values(), *self.layers, *self.embed_extras]
         if self.logit_transform is not None:
             stack.append(self.logit_transform)
         while stack:
@@ -139,6 +146,8 @@ class DecoderModel:
         self.embed = tensors[spec.embed_name]
         head = None if spec.tie_embeddings or not spec.lm_head_name else tensors.get(spec.lm_head_name)
         self.lm_head = head if head is not None else self.embed
+        for part in self.embed_extras:
+            part.bind({k: tensors[k] for k in part.tensors() if k in tensors}, ops)
         for ls, block in zip(spec.layers, self.layers):
             block.bind({k[len(ls.prefix):]: v for k, v in tensors.items() if k.startswith(ls.prefix)}, ops)
         stem = spec.final_norm_name.rsplit(".", 1)[0] + "."

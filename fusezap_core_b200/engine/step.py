@@ -236,6 +236,7 @@ class StepRunner:
                 lc.group, lc.page_size = g, cache.page_size
             lc.state = {name: t for (entry, name), t in cache.states.tensors.items() if entry == n}
             self.layer_caches.append(lc)
+        self.embed_state = {name: t for (entry, name), t in cache.states.tensors.items() if entry == -1}
 
     def forward(self, ids_out: torch.Tensor | None = None) -> torch.Tensor | None:
         """Runs the model over the metadata already filled; returns logits (n_wanted, vocab) float32. With `ids_out`
@@ -264,6 +265,8 @@ class StepRunner:
             if src is not None:      # some rows take their token from the ids the previous step left on the device
                 ctx.token_ids = self.ws.get("token_ids", (meta.n_rows,), torch.int32)
                 self.ops.select_tokens(meta.tokens, src, self.prev_ids, ctx.token_ids)
+        for part in model.embed_extras:
+            part.forward(ctx, x, self.embed_state)
         delta = None
         for e, lc in zip(spec.schedule, self.layer_caches):
             x, delta = model.layers[e.layer].forward(ctx, x, delta, lc)

@@ -157,7 +157,39 @@ class Ops:
     def head_norm_gate(self, o: torch.Tensor, heads: int, value_dim: int, weight: torch.Tensor | None, eps: float,
                        gate: torch.Tensor | None, gate_offset: int, activation: str | None, out: torch.Tensor) -> None:
         """o: (N, H dv) float32. out[n, h, c] = T(o / sqrt(mean_c(o[n, h]^2) + eps) * weight[c] * act(gate[n, gate_offset +
-        h dv + c])); weight (dv,) float32 or None (1); gate float32 (N, any width) or None (1); act "silu", "sigmoid"."""
+        h dv + c])); weight (dv,) float32, shared by the heads, or (H dv,), one per head and channel (weight[h dv + c]),
+        or None (1); gate float32 (N, any width) or None (1); act "silu", "sigmoid"."""
+        raise NotImplementedError
+
+    def general_delta_scan(self, proj: torch.Tensor, heads: int, key_dim: int, value_dim: int, remove_offset: int,
+                           decay_in: torch.Tensor, decay_bias: torch.Tensor, remove_bias: torch.Tensor, decay_rate: float,
+                           unit_eps: float, state: torch.Tensor, meta: Any, out: torch.Tensor) -> None:
+        """proj: (N, ld) float32, a row = [r (H dk) | k (H dk) | v (H dv) | ...] with the removal inputs (H dk) from
+        column remove_offset on; decay_in (N, H dk) float32; decay_bias, remove_bias (H dk,) float32. Per portion, token
+        by token, per head: u = k / sqrt(sum k^2 + unit_eps), d = exp(-decay_rate * sigmoid(decay_in + decay_bias)),
+        a = sigmoid(remove + remove_bias) per key channel; with b = S^T u of the state before the token,
+        S = diag(d) S - (a * u) b^T + k v^T, out[n, h] = S^T r. float32 throughout; out (N, H dv); the state
+        (`recurrent_state_shape`) is that after the portion's last token. Padding rows give zeros."""
+        raise NotImplementedError
+
+    def activate(self, src: torch.Tensor, offset: int, kind: str, out: torch.Tensor) -> None:
+        """out[n, j] = T(act(src[n, offset + j])) for the columns of out; src float32 (N, any width); kind "tanh",
+        "sigmoid", "silu", "gelu_tanh", computed in float32 and rounded once. Padding rows need not be zero."""
+        raise NotImplementedError
+
+    def hashed_pair_embed(self, table: torch.Tensor, token_ids: torch.Tensor, meta: Any, state: torch.Tensor,
+                          buckets: int, mul_prev: int, mul_cur: int, x: torch.Tensor) -> None:
+        """table: (buckets + 1, D) T; token_ids int32 (N,); state int32 (slots, 1); x (N, D) float32. For the row at
+        place i of its portion (meta.seg), at position p: x += float32(table[r]) with r = buckets if p = 0, else
+        (u * mul_prev + t * mul_cur) mod buckets in 64-bit integers, t the row's token and u the token of the row before
+        (i > 0) or state[slot] (i = 0). Afterwards state[slot] holds the portion's last token. Padding rows are left."""
+        raise NotImplementedError
+
+    def depth_average(self, streams: torch.Tensor, depth: int, coef: torch.Tensor | None, x: torch.Tensor,
+                      delta: torch.Tensor | None) -> None:
+        """streams: (N, L + 1, D) float32; x, delta (N, D) float32 (delta None: zero). streams[:, depth + 1] = x + delta;
+        then x = sum_j coef[j] * streams[:, j] over j = 0 .. depth + 1 in rising j (coef float32, depth + 2 numbers),
+        each product rounded, in float32. depth -1 with coef None: streams[:, 0] = x + delta and x = x + delta."""
         raise NotImplementedError
 
     def check_sink_attention(self, num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int) -> None:
@@ -166,19 +198,25 @@ class Ops:
 
     def rotate_kv_write(self, qkv: torch.Tensor, cos: torch.Tensor | None, sin: torch.Tensor | None, rotated: int,
                         pairing: int, meta: Any, cache: Any, q_out: torch.Tensor, num_heads: int, num_kv_heads: int,
-                        key_dim: int, value_dim: int) -> None:
-        """qkv: (N, Hq dk + Hkv dk + Hkv dv) float32 = [q | k | v]. The first `rotated` dimensions of every q and k head
+                        key_dim: int, value_dim: int, q_norm: torch.Tensor | None = None, k_norm: torch.Tensor | None = None,
+                        norm_eps: float = 0.0, query_temperature: tuple | None = None) -> None:
+        """qkv: (N, >= Hq dk + Hkv dk + Hkv dv) float32 = [q | k | v | anything] (with cache.write False only the q
+        columns are read and the row may be as short as Hq dk). The first `rotated` dimensions of every q and k head
         are turned by the row's position (pairing as in `retention_scan`), the rest pass; q goes to q_out (N, Hq dk) T,
         k and v, rounded once, to the row's place in its request's pages (cache.keys (pages, Hkv, page, dk),
-        cache.values (pages, Hkv, page, dv), any strides with a unit last one)."""
+        cache.values (pages, Hkv, page, dv), any strides with a unit last one). q_norm / k_norm (dk,) float32: before the
+        rotation every q / k head becomes x / sqrt(mean(x^2) + norm_eps) * weight. query_temperature (coef, every): after
+        the rotation q at position p is multiplied by 1 + coef * ln(floor((p + 1) / every) + 1). All in float32."""
         raise NotImplementedError
 
     def sink_attention(self, q: torch.Tensor, cache: Any, meta: Any, out: torch.Tensor, num_heads: int, num_kv_heads: int,
                        key_dim: int, value_dim: int, scale: float, window: int, keep_first: int,
-                       sink: torch.Tensor | None) -> None:
-        """out[n, h] = sum_j e_j v_j / (sum_j e_j + exp(sink[h] - m)), e_j = exp((q[n, h] . k_j) * scale - m), over the
-        keys j <= p of the row's own request with p - j < window or j < keep_first (window 0: all), p = meta.pos[n], m
-        the largest of the scores and sink[h]; sink None: no such term. kv head h // (Hq / Hkv). out: (N, Hq dv) T."""
+                       sink: torch.Tensor | None, softcap: float = 0.0, gate: tuple | None = None) -> None:
+        """out[n, h] = sum_j e_j v_j / (sum_j e_j + exp(sink[h] - m)), e_j = exp(s_j - m), s_j = (q[n, h] . k_j) * scale,
+        over the keys j <= p of the row's own request with p - j < window or j < keep_first (window 0: all), p =
+        meta.pos[n], m the largest of the scores and sink[h]; sink None: no such term. kv head h // (Hq / Hkv).
+        out: (N, Hq dv) T. softcap c > 0: s_j = c * tanh((q . k_j) * scale / c). gate (g, offset), g float32 (N, any
+        width): out[n, h] is multiplied by sigmoid(g[n, offset + h]) before it is rounded."""
         raise NotImplementedError
 
     def weighted_sum(self, terms: list, weights: list, out: torch.Tensor) -> None:
@@ -212,8 +250,9 @@ class Ops:
         returns None if this table has no fused kernel for these sizes (the part then runs `linear` + `swiglu`)."""
         return None
 
-    def linear_swiglu(self, a: torch.Tensor, packed: Any, out: torch.Tensor) -> None:
-        """out[m, i] = T(silu(a[m] . gate[i] + gate_bias[i]) * (a[m] . up[i] + up_bias[i])); `packed` from `pack_gate_up`.
+    def linear_swiglu(self, a: torch.Tensor, packed: Any, out: torch.Tensor, activation: str = "silu") -> None:
+        """out[m, i] = T(act(a[m] . gate[i] + gate_bias[i]) * (a[m] . up[i] + up_bias[i])); `packed` from `pack_gate_up`;
+        act as in `swiglu`.
         The products are accumulated in float32 and are not rounded before the activation."""
         raise NotImplementedError
 
@@ -238,8 +277,9 @@ class Ops:
         max(0, p - window + 1) <= j <= p (window 0: 0 <= j <= p), p = meta.pos[n]; kv head h // (Hq / Hkv)."""
         raise NotImplementedError
 
-    def swiglu(self, gate_up: torch.Tensor, out: torch.Tensor) -> None:
-        """gate_up: (N, 2 I) T = [gate | up]; out[n, i] = T(silu(gate[n, i]) * up[n, i]), silu in float32."""
+    def swiglu(self, gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> None:
+        """gate_up: (N, 2 I) T = [gate | up]; out[n, i] = T(act(gate[n, i]) * up[n, i]), act in float32: "silu", or
+        "gelu_tanh": 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))."""
         raise NotImplementedError
 
     def linear_argmax(self, a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor) -> bool:

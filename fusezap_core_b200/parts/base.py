@@ -12,8 +12,10 @@ through the kernel table of the step (`ctx.ops`), taking scratch buffers from `c
   PositionEncoding.rotate_and_store(ctx, qkv, q_out, cache, num_heads, num_kv_heads, head_dim)
   Block.forward(ctx, x, delta, cache) -> (x, delta)   the arrangement of norms, mixer and feed-forward of one layer
   LogitTransform.forward(ctx, logits) -> None    changes the float32 logits of the wanted rows in place
+  EmbedExtra.forward(ctx, x, state) -> None      adds to the gathered embeddings x (N, D) float32 before the first layer
 
-Register a new part with `@register_mixer("name")` (or _feed_forward, _norm, _position, _block, _logit_transform) and name it in a
+Register a new part with `@register_mixer("name")` (or _feed_forward, _norm, _position, _block, _logit_transform,
+_embed_extra) and name it in a
 `PartSpec`; nothing else in the package changes.
 """
 from __future__ import annotations
@@ -35,6 +37,7 @@ NORMS: dict[str, type] = {}
 POSITIONS: dict[str, type] = {}
 BLOCKS: dict[str, type] = {}
 LOGIT_TRANSFORMS: dict[str, type] = {}
+EMBED_EXTRAS: dict[str, type] = {}
 
 
 def _register(table: dict[str, type], what: str) -> Callable[[str], Callable[[type], type]]:
@@ -53,6 +56,7 @@ register_norm = _register(NORMS, "norm")
 register_position = _register(POSITIONS, "position encoding")
 register_block = _register(BLOCKS, "block")
 register_logit_transform = _register(LOGIT_TRANSFORMS, "logit transform")
+register_embed_extra = _register(EMBED_EXTRAS, "embedding extra")
 
 
 def build(table: dict[str, type], what: str, spec: PartSpec) -> Any:
@@ -168,4 +172,16 @@ class LogitTransform(Part):
     the model the output product always writes its logits (no fused argmax), unless the transform sets `keeps_order`
     (it never changes which logit of a row is the largest)."""
     def forward(self, ctx: "StepContext", logits: torch.Tensor) -> None:
+        raise NotImplementedError
+
+
+class EmbedExtra(Part):
+    """Adds to the gathered embeddings, x (N, D) float32, in place, before the first layer runs. It names its tensors in
+    full (they belong to no layer), may keep per-request state of fixed size (`state_need()`, as a mixer does; `state`
+    in `forward` maps each name to its (slots, *shape) tensor), and reads the step's token ids from `ctx.token_ids` if
+    it declares the step need "token_ids"."""
+    def state_need(self) -> dict[str, Any]:
+        return {}
+
+    def forward(self, ctx: "StepContext", x: torch.Tensor, state: dict[str, torch.Tensor]) -> None:
         raise NotImplementedError

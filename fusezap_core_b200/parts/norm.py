@@ -15,20 +15,22 @@ from .base import Norm, register_norm
 
 @register_norm("rmsnorm")
 class RMSNorm(Norm):
-    def __init__(self, size: int, eps: float, groups: int = 1, name: str = "weight"):
+    def __init__(self, size: int, eps: float, groups: int = 1, name: str = "weight", scalar: bool = False):
         """groups: the vector is split into this many equal consecutive parts and each is divided by its own root mean
         square (1: the whole vector). name: the weight's tensor name relative to the part ("" when the part's prefix is
-        the whole name)."""
+        the whole name). scalar: the weight is one number for all coordinates (a tensor without dimensions)."""
         if groups <= 0 or size % groups:
             raise ValueError(f"a norm over {size} values cannot be split into {groups} equal groups")
-        self.size, self.eps, self.groups, self.name = size, float(eps), int(groups), name
+        self.size, self.eps, self.groups, self.name, self.scalar = size, float(eps), int(groups), name, bool(scalar)
         self.weight: torch.Tensor | None = None
 
     def tensors(self) -> dict[str, ParamSpec]:
-        return {self.name: ParamSpec((self.size,), role="vector", init="ones")}
+        return {self.name: ParamSpec(() if self.scalar else (self.size,), role="vector", init="ones")}
 
     def bind(self, tensors, ops) -> None:
         self.weight = tensors[self.name]
+        if self.scalar:      # the kernels take a weight per coordinate
+            self.weight = self.weight.float().reshape(1).expand(self.size).contiguous()
 
     def forward(self, ctx, x, delta, rows=None, n_rows=None):
         n = x.shape[0] if rows is None else (n_rows if n_rows is not None else rows.shape[0])

@@ -40,16 +40,22 @@ def inverse_frequencies(head_dim: int, theta: float, kind: str = "default", fact
 class RotaryEncoding(PositionEncoding):
     def __init__(self, head_dim: int, theta: float, kind: str = "default", factor: float = 1.0,
                  low_freq_factor: float = 1.0, high_freq_factor: float = 4.0,
-                 original_max_position_embeddings: int = 0, precise: bool = False):
+                 original_max_position_embeddings: int = 0, precise: bool = False, turns_fast: float = 32.0,
+                 turns_slow: float = 1.0, magnitude: float = 1.0):
         """precise: frequencies theta^(-2j/head_dim) and angles p * f_j are computed in 64-bit and the cosines and sines
         rounded once to float32 (default: in float32 throughout, as the dense decoder's reference does). The tables
         serve any pairing of dimensions: a mixer that rotates in its own kernels (neighbouring dimensions paired, only
-        the first dimensions of a head rotated) reads `cos` / `sin` (max_len, head_dim / 2) by pair index."""
+        the first dimensions of a head rotated) reads `cos` / `sin` (max_len, head_dim / 2) by pair index.
+        kind "yarn" (factor, original_max_position_embeddings, turns_fast, turns_slow): see below; `magnitude`
+        multiplies both tables (1: plain cosines and sines)."""
         if head_dim % 2:
             raise ValueError(f"rope needs an even head_dim, got {head_dim}")
         self.head_dim, self.precise = head_dim, bool(precise)
-        if precise and kind not in ("default", "llama3"):
-            raise NotImplementedError("precise angles are computed for unscaled and for llama3-scaled frequencies only")
+        if precise and kind not in ("default", "llama3", "yarn"):
+            raise NotImplementedError("precise angles are computed for unscaled, llama3-scaled and yarn-scaled frequencies only")
+        if kind == "yarn" and not precise:
+            raise NotImplementedError("yarn-scaled frequencies are computed in 64-bit only (precise=True)")
+        self.magnitude = float(magnitude)
         self.inv_freq64 = np.float64(theta) ** (-np.arange(0, head_dim, 2, dtype=np.float64) / np.float64(head_dim))
         if precise and kind == "llama3":
             # by wavelength l = 2 pi / f: short ones (l < old / high) stay, long ones (l > old / low) are divided by
@@ -59,8 +65,19 @@ class RotaryEncoding(PositionEncoding):
             s = (old / wl - low_freq_factor) / (high_freq_factor - low_freq_factor)
             self.inv_freq64 = np.where(wl < old / high_freq_factor, f,
                                        np.where(wl > old / low_freq_factor, f / factor, (1 - s) * f / factor + s * f))
-        self.inv_freq = inverse_frequencies(head_dim, theta, kind, factor, low_freq_factor, high_freq_factor,
-                                            original_max_position_embeddings)
+        if kind == "yarn":
+            # by the pair index at which a frequency makes `turns` full turns over the original length,
+            # dim(t) = head_dim ln(old / (2 pi t)) / (2 ln theta): pairs below dim(turns_fast) keep their frequency,
+            # pairs above dim(turns_slow) are divided by `factor`, those between are blended linearly in the index
+            old = float(original_max_position_embeddings)
+            def pair_of(turns: float) -> float:
+                return head_dim * math.log(old / (2 * math.pi * turns)) / (2 * math.log(theta))
+            lo = max(math.floor(pair_of(turns_fast)), 0)
+            hi = min(math.ceil(pair_of(turns_slow)), head_dim - 1)
+            ramp = np.clip((np.arange(head_dim // 2, dtype=np.float64) - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+            self.inv_freq64 = self.inv_freq64 / factor * ramp + self.inv_freq64 * (1.0 - ramp)
+        self.inv_freq = None if kind == "yarn" else inverse_frequencies(
+            head_dim, theta, kind, factor, low_freq_factor, high_freq_factor, original_max_position_embeddings)
         self.cos: torch.Tensor | None = None
         self.sin: torch.Tensor | None = None
 
@@ -69,8 +86,8 @@ class RotaryEncoding(PositionEncoding):
             fr = np.arange(max_len, dtype=np.float64)[:, None] * self.inv_freq64[None, :]
         else:
             fr = np.arange(max_len, dtype=np.float32)[:, None] * self.inv_freq[None, :]
-        self.cos = torch.from_numpy(np.cos(fr).astype(np.float32)).to(device)
-        self.sin = torch.from_numpy(np.sin(fr).astype(np.float32)).to(device)
+        self.cos = torch.from_numpy((np.cos(fr) * self.magnitude).astype(np.float32)).to(device)
+        self.sin = torch.from_numpy((np.sin(fr) * self.magnitude).astype(np.float32)).to(device)
 
     def weight_tensors(self) -> list:
         return []       # a step gathers one row of the tables per token; they are not streamed like weights

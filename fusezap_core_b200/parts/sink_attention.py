@@ -11,6 +11,16 @@ q and k are rotated by position on their first `rotated` dimensions (`pairing` "
 i with i + rotated/2), v is not. One product with the rows [q; k; v] leaves float32; the rotation, scores, softmax and
 the value sum are 32-bit in both dtypes; keys and values are rounded once into the paged cache. The cache group of this
 mixer gives back pages that lie wholly between the kept first tokens and the window.
+
+Options, all off by default: `bias` names the products that have one (of "q", "k", "v", "out"; tensor `<name><bias_suffix>`);
+`qk_norm`: every q and k head is divided by its root mean square (`norm_eps` inside the root) and multiplied by a weight
+of key_dim values shared by the heads (`<q><norm_suffix>`, `<k><norm_suffix>`), before the rotation; `query_temperature`
+(coef, every): q at position p is multiplied by `1 + coef * ln(floor((p + 1) / every) + 1)`; `softcap` c > 0: the scaled
+score s becomes `c * tanh(s / c)`; `head_gate`: head h's output is multiplied by `sigmoid(W_gate h)_h`, one number per
+head, before the output product; `own_kv=False`: the layer has no key and value projections and reads, with queries of
+its own, the cache that another layer's mixer wrote (its schedule entry names that cache slot); `cache_window`: the
+window the cache must keep when other layers read it too (None: this mixer's own). The norms, the temperature, the cap
+and the gate are 32-bit in both dtypes.
 """
 from __future__ import annotations
 import torch
@@ -20,14 +30,16 @@ from ..weights import ParamSpec
 from .base import LayerCache, Mixer, register_mixer
 from .retention import PAIRINGS
 
-_NAMES = {"q": "q_proj", "k": "k_proj", "v": "v_proj", "sink": "sinks", "out": "o_proj"}
+_NAMES = {"q": "q_proj", "k": "k_proj", "v": "v_proj", "sink": "sinks", "out": "o_proj", "gate": "g_proj"}
 
 
 @register_mixer("sink_attention")
 class SinkAttention(Mixer):
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int, scale: float,
                  window: int = 0, keep_first: int = 0, sink: bool = True, rotated: int = 0, pairing: str = "neighbours",
-                 position: str | None = None, names: dict | None = None):
+                 position: str | None = None, names: dict | None = None, bias: tuple = (), bias_suffix: str = ".bias",
+                 qk_norm: bool = False, norm_eps: float = 1e-6, norm_suffix: str = "_norm", query_temperature: tuple | None = None,
+                 softcap: float = 0.0, head_gate: bool = False, own_kv: bool = True, cache_window: int | None = None):
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} query heads are not a multiple of {num_kv_heads} kv heads")
         if pairing not in PAIRINGS:
@@ -38,25 +50,62 @@ class SinkAttention(Mixer):
         self.scale, self.window, self.keep_first, self.has_sink = float(scale), int(window), int(keep_first), bool(sink)
         self.rotated, self.pairing, self.position = int(rotated), pairing, (position if rotated else None)
         self.names = {**_NAMES, **(names or {})}
-        self.wqkv = self.wo = self.sink = None
+        if not set(bias) <= {"q", "k", "v", "out"}:
+            raise ValueError(f"bias {bias!r} names something else than the q, k, v and out products")
+        if query_temperature is not None and int(query_temperature[1]) <= 0:
+            raise ValueError(f"query temperature {query_temperature!r}: the period must be positive")
+        self.bias, self.bias_suffix = tuple(bias), bias_suffix
+        self.qk_norm, self.norm_eps, self.norm_suffix = bool(qk_norm), float(norm_eps), norm_suffix
+        self.q_temp = (float(query_temperature[0]), int(query_temperature[1])) if query_temperature is not None else None
+        self.softcap, self.head_gate, self.own_kv = float(softcap), bool(head_gate), bool(own_kv)
+        self.cache_window = self.window if cache_window is None else int(cache_window)
+        if self.cache_window and (not self.window or self.cache_window < self.window):
+            raise ValueError(f"a cache that keeps {self.cache_window} tokens cannot serve a window of {self.window or 'all'}")
+        self.wqkv = self.bqkv = self.wo = self.bo = self.sink = self.q_norm_w = self.k_norm_w = None
 
     def tensors(self) -> dict[str, ParamSpec]:
         n = self.names
-        out = {n["q"]: ParamSpec((self.Hq * self.dk, self.D)), n["k"]: ParamSpec((self.Hkv * self.dk, self.D)),
-               n["v"]: ParamSpec((self.Hkv * self.dv, self.D)), n["out"]: ParamSpec((self.D, self.Hq * self.dv))}
+        rows = {"q": self.Hq * self.dk, "k": self.Hkv * self.dk, "v": self.Hkv * self.dv, "out": self.D}
+        out = {n["q"]: ParamSpec((rows["q"], self.D)), n["out"]: ParamSpec((self.D, self.Hq * self.dv))}
+        if self.own_kv:
+            out[n["k"]] = ParamSpec((rows["k"], self.D))
+            out[n["v"]] = ParamSpec((rows["v"], self.D))
+        for x in self.bias:
+            if self.own_kv or x not in ("k", "v"):
+                out[n[x] + self.bias_suffix] = ParamSpec((rows[x],), role="vector")
+        if self.qk_norm:
+            out[n["q"] + self.norm_suffix] = ParamSpec((self.dk,), role="vector", init="ones")
+            if self.own_kv:
+                out[n["k"] + self.norm_suffix] = ParamSpec((self.dk,), role="vector", init="ones")
+        if self.head_gate:
+            out[n["gate"]] = ParamSpec((self.Hq, self.D))
         if self.has_sink:
             out[n["sink"]] = ParamSpec((self.Hq,), role="vector")
         return out
 
     def bind(self, tensors, ops) -> None:
         n = self.names
-        self.wqkv = torch.cat([tensors[n["q"]], tensors[n["k"]], tensors[n["v"]]], 0).contiguous()
+        # one product for everything that reads h: columns [q | k | v | gate] (k and v only with projections of its own)
+        parts = ["q"] + (["k", "v"] if self.own_kv else []) + (["gate"] if self.head_gate else [])
+        self.wqkv = torch.cat([tensors[n[x]] for x in parts], 0).contiguous()
+        self.bqkv = None
+        if set(self.bias) & set(parts):
+            self.bqkv = torch.cat([tensors[n[x] + self.bias_suffix].float() if x in self.bias else
+                                   torch.zeros(tensors[n[x]].shape[0], dtype=torch.float32, device=self.wqkv.device)
+                                   for x in parts], 0).contiguous()
+        self.width = self.wqkv.shape[0]
+        self.off_gate = self.width - self.Hq
         self.wo = tensors[n["out"]]
+        self.bo = tensors[n["out"] + self.bias_suffix].float().contiguous() if "out" in self.bias else None
         self.sink = tensors[n["sink"]].float().contiguous() if self.has_sink else None
+        if self.qk_norm:
+            self.q_norm_w = tensors[n["q"] + self.norm_suffix].float().contiguous()
+            self.k_norm_w = tensors[n["k"] + self.norm_suffix].float().contiguous() if self.own_kv else None
         ops.check_sink_attention(self.Hq, self.Hkv, self.dk, self.dv)
 
     def cache_need(self) -> KVNeed:
-        return KVNeed(self.Hkv, self.dk, self.window, value_dim=self.dv, keep_first=self.keep_first if self.window else 0)
+        return KVNeed(self.Hkv, self.dk, self.cache_window, value_dim=self.dv,
+                      keep_first=self.keep_first if self.cache_window else 0)
 
     def position_name(self) -> str | None:
         return self.position
@@ -67,14 +116,27 @@ class SinkAttention(Mixer):
     def forward(self, ctx, h: torch.Tensor, cache: LayerCache) -> torch.Tensor:
         n, ops, ws = h.shape[0], ctx.ops, ctx.ws
         Hq, Hkv, dk, dv = self.Hq, self.Hkv, self.dk, self.dv
-        qkv = ws.get("sink_qkv", (n, (Hq + Hkv) * dk + Hkv * dv), torch.float32)
-        ops.linear(h, self.wqkv, None, qkv)
+        if cache.write != self.own_kv:
+            raise ValueError("a mixer with key and value projections of its own writes its cache slot, one without reads "
+                             "another layer's: the schedule entry says otherwise")
+        qkv = ws.get("sink_qkv", (n, self.width), torch.float32)
+        ops.linear(h, self.wqkv, self.bqkv, qkv)
         q = ws.get("sink_q", (n, Hq * dk), ops.dtype)
         pos = ctx.positions[self.position] if self.position is not None else None
-        ops.rotate_kv_write(qkv, pos.cos if pos else None, pos.sin if pos else None, self.rotated, PAIRINGS[self.pairing],
-                            ctx.meta, cache, q, Hq, Hkv, dk, dv)
+        plain = not (self.qk_norm or self.q_temp or self.head_gate) and self.own_kv
+        if plain:
+            ops.rotate_kv_write(qkv, pos.cos if pos else None, pos.sin if pos else None, self.rotated, PAIRINGS[self.pairing],
+                                ctx.meta, cache, q, Hq, Hkv, dk, dv)
+        else:
+            ops.rotate_kv_write(qkv, pos.cos if pos else None, pos.sin if pos else None, self.rotated, PAIRINGS[self.pairing],
+                                ctx.meta, cache, q, Hq, Hkv, dk, dv, q_norm=self.q_norm_w, k_norm=self.k_norm_w,
+                                norm_eps=self.norm_eps, query_temperature=self.q_temp)
         o = ws.get("sink_out", (n, Hq * dv), ops.dtype)
-        ops.sink_attention(q, cache, ctx.meta, o, Hq, Hkv, dk, dv, self.scale, self.window, self.keep_first, self.sink)
+        if self.softcap or self.head_gate:
+            ops.sink_attention(q, cache, ctx.meta, o, Hq, Hkv, dk, dv, self.scale, self.window, self.keep_first, self.sink,
+                               softcap=self.softcap, gate=(qkv, self.off_gate) if self.head_gate else None)
+        else:
+            ops.sink_attention(q, cache, ctx.meta, o, Hq, Hkv, dk, dv, self.scale, self.window, self.keep_first, self.sink)
         delta = ws.get("sink_delta", (n, self.D), torch.float32)
-        ops.linear(o, self.wo, None, delta)
+        ops.linear(o, self.wo, self.bo, delta)
         return delta

@@ -45,7 +45,7 @@ def draw(rng: np.random.Generator, p: ParamSpec, norm_noise: bool, optional: boo
         a = np.zeros(p.shape, np.float32)
     else:
         a = rng.standard_normal(p.shape, dtype=np.float32) * np.float32(STD)
-    return torch.from_numpy(a)
+    return torch.from_numpy(np.asarray(a, np.float32))      # (a tensor without dimensions comes out of the arithmetic as a scalar)
 
 
 def random_tensors(expected: dict[str, ParamSpec], seed: int, dtype: str = "float32", norm_noise: bool = False,

@@ -1,0 +1,95 @@
+"""Small Nepudra configurations shared by the CPU and GPU tests of that design.
+
+They differ from one another in every size and constant and keep apart what a model could make equal: key and value
+sizes unequal, heads rotated in part and in whole, grouped and ungrouped heads, windows shorter and longer than a page,
+temperature periods of a few tokens, caps near the scores' size, every order of the three layer types, layers without
+feed-forward, a cache read by one and by two later layers, with and without frequency scaling."""
+from __future__ import annotations
+import copy
+import os
+
+import numpy as np
+import torch
+
+
+def _att(heads, kv, dim, vdim, scale, coef, every, cap, kv_from=None):
+    m = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": vdim, "scale": scale, "q_temp": {"coef": coef, "every": every},
+         "softcap": cap}
+    if kv_from is not None:
+        m["kv_from"] = kv_from
+    return m
+
+
+def _att2(heads, kv, dim, vdim, scale, size, base, dims, scaling=None):
+    rot = {"base": base, "dims": dims}
+    if scaling:
+        rot["scaling"] = dict(zip(("factor", "original", "fast", "slow"), scaling))
+    return {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": vdim, "scale": scale, "mask": {"size": size}, "rot": rot}
+
+
+def _layer(kind, mixer, ff):
+    return {"type": kind, "mixer": mixer, "mlp": {"kind": "dense", "ff": ff} if ff else None}
+
+
+NEP_MIX = {       # window first; a cache read by a later layer; the recurrence in the middle; partly rotated heads
+    "architecture": "Nepudra", "vocab": 173, "width": 64, "norm": {"eps": 1e-5},
+    "embedding": {"bigram": {"buckets": 97, "mul_prev": 7, "mul_cur": 3}},
+    "layers": [
+        _layer("attention_2", _att2(4, 2, 16, 8, 0.3, 9, 5000.0, 8, (4.0, 16, 4.0, 0.5)), 48),
+        _layer("attention", _att(4, 1, 8, 24, 0.4, 0.7, 5, 2.5), 40),
+        _layer("general_delta", {"heads": 2, "dim": 12}, 0),
+        _layer("attention", _att(4, 1, 8, 24, 0.25, 0.3, 3, 4.0, kv_from=1), 24),
+    ]}
+NEP_ODD = {       # the recurrence first; sizes that are no multiples of 16; ungrouped heads; a window shorter than a page;
+                  # unscaled frequencies on whole heads; two readers of one cache; an attention layer without feed-forward
+    "architecture": "Nepudra", "vocab": 89, "width": 96, "norm": {"eps": 1e-6},
+    "embedding": {"bigram": {"buckets": 211, "mul_prev": 1, "mul_cur": 13}},
+    "layers": [
+        _layer("general_delta", {"heads": 3, "dim": 20}, 56),
+        _layer("attention", _att(3, 3, 24, 40, 0.2, 1.5, 7, 1.0), 0),
+        _layer("attention_2", _att2(2, 2, 12, 20, 0.35, 5, 300.0, 12), 24),
+        _layer("attention", _att(3, 3, 24, 40, 0.15, 0.1, 2, 30.0, kv_from=1), 32),
+        _layer("attention", _att(3, 3, 24, 40, 0.3, 0.9, 11, 0.75, kv_from=1), 0),
+    ]}
+NEP_ONE = {       # a single head everywhere; a long window; one layer of each kind
+    "architecture": "Nepudra", "vocab": 61, "width": 32, "norm": {"eps": 1e-4},
+    "embedding": {"bigram": {"buckets": 30, "mul_prev": 5, "mul_cur": 1}},
+    "layers": [
+        _layer("attention", _att(1, 1, 32, 16, 0.25, 0.4, 4, 6.0), 40),
+        _layer("attention_2", _att2(6, 1, 8, 8, 0.35, 33, 20.0, 2, (8.0, 64, 2.0, 1.0)), 0),
+        _layer("general_delta", {"heads": 1, "dim": 40}, 16),
+    ]}
+CONFIGS = {"mix": (NEP_MIX, 3), "odd": (NEP_ODD, 5), "one": (NEP_ONE, 9)}
+STD_SCALE = 5.0
+
+
+def make_dir(name: str, tmp, cfg: dict | None = None, seed: int | None = None, change=None) -> tuple[str, dict, dict]:
+    """Writes configuration `name` with seeded random weights (float32); `change(tensors)` may edit them before they
+    are written. Returns (folder, config, weights by name)."""
+    from fusezap_core_b200.weights import write_random_model
+    from fusezap_core_b200.weights.safetensors_io import read_model_dir, write_file
+    base, s = CONFIGS.get(name, (cfg, seed))
+    cfg = copy.deepcopy(cfg if cfg is not None else base)
+    d = os.path.join(str(tmp), f"nepudra-{name}")
+    write_random_model(cfg, d, seed if seed is not None else s, "float32", norm_noise=True, std_scale=STD_SCALE)
+    w = read_model_dir(d)
+    if change is not None:
+        w = {k: v.clone() for k, v in w.items()}
+        change(w)
+        write_file(os.path.join(d, "model.safetensors"), w)
+    return d, cfg, w
+
+
+def tokens_for(cfg: dict, lengths, seed: int) -> list[list[int]]:
+    rng = np.random.default_rng(seed)
+    return [rng.integers(0, cfg["vocab"], n).tolist() for n in lengths]
+
+
+def plain_logits(cfg: dict, w: dict, toks) -> np.ndarray:
+    import plain_nepudra
+    return plain_nepudra.forward(cfg, {k: v.double() for k, v in w.items()}, list(toks)).numpy()
+
+
+def rounded(w: dict) -> dict:
+    """The weights as a bfloat16 engine holds them: matrices rounded once, vectors stored in 32-bit as they are."""
+    return {k: v.to(torch.bfloat16).to(torch.float32) if v.dim() >= 2 else v for k, v in w.items()}

@@ -404,3 +404,136 @@ class PlainOpsSeq(PlainOpsWide):
         if shared is not None:
             acc = acc + torch.sigmoid(gate_logits[:, gate_column: gate_column + 1]) * shared
         out.copy_(acc)
+
+
+class PlainOpsDeep(PlainOpsSeq):
+    """The operations of depth-averaged layers, the hashed pair embedding, the generalized delta rule and the attention
+    with head gates, capped scores, normed queries and keys and a query temperature."""
+
+    @staticmethod
+    def _act(z, kind):
+        if kind == "tanh":
+            return torch.tanh(z)
+        if kind == "sigmoid":
+            return torch.sigmoid(z)
+        if kind == "silu":
+            return z * torch.sigmoid(z)
+        if kind == "gelu_tanh":
+            return 0.5 * z * (1 + torch.tanh(0.7978845608028654 * (z + 0.044715 * z ** 3)))
+        raise ValueError(kind)
+
+    def swiglu(self, gate_up, out, activation="silu") -> None:
+        I = out.shape[1]
+        g, u = gate_up[:, :I].float(), gate_up[:, I:].float()
+        out.copy_((self._act(g, activation) * u).to(out.dtype))
+
+    def activate(self, src, offset, kind, out) -> None:
+        out.copy_(self._act(src[:, offset: offset + out.shape[1]].float(), kind).to(out.dtype))
+
+    def head_norm_gate(self, o, heads, value_dim, weight, eps, gate, gate_offset, activation, out):
+        if weight is not None and weight.shape[0] == heads * value_dim:
+            n = o.shape[0]
+            x = o.view(n, heads, value_dim)
+            y = x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * weight.float().view(heads, value_dim)
+            z = gate[:, gate_offset: gate_offset + heads * value_dim].reshape(n, heads, value_dim)
+            out.copy_((y * self._act(z, activation)).reshape(n, -1).to(out.dtype))
+        else:
+            super().head_norm_gate(o, heads, value_dim, weight, eps, gate, gate_offset, activation, out)
+
+    def hashed_pair_embed(self, table, token_ids, meta, state, buckets, mul_prev, mul_cur, x) -> None:
+        ids = token_ids.long()
+        for sg in meta.segments:
+            for i in range(sg.n):
+                n = sg.row0 + i
+                if sg.pos0 + i == 0:
+                    r = buckets
+                else:
+                    prev = int(ids[n - 1]) if i > 0 else int(state[sg.state_slot, 0])
+                    r = (prev * mul_prev + int(ids[n]) * mul_cur) % buckets
+                x[n] += table[r].float()
+            state[sg.state_slot, 0] = ids[sg.row0 + sg.n - 1].to(state.dtype)
+
+    def depth_average(self, streams, depth, coef, x, delta) -> None:
+        if delta is not None:
+            x += delta
+        streams[:, depth + 1] = x
+        if coef is not None:
+            acc = torch.zeros_like(x)
+            for j in range(depth + 2):
+                acc = acc + coef[j] * streams[:, j]
+            x.copy_(acc)
+
+    def general_delta_scan(self, proj, heads, key_dim, value_dim, remove_offset, decay_in, decay_bias, remove_bias, decay_rate,
+                           unit_eps, state, meta, out) -> None:
+        H, dk, dv = heads, key_dim, value_dim
+        out.zero_()
+        for sg in meta.segments:
+            rows = slice(sg.row0, sg.row0 + sg.n)
+            x = proj[rows].double()
+            r = x[:, :H * dk].reshape(-1, H, dk)
+            k = x[:, H * dk: 2 * H * dk].reshape(-1, H, dk)
+            v = x[:, 2 * H * dk: 2 * H * dk + H * dv].reshape(-1, H, dv)
+            a = torch.sigmoid(x[:, remove_offset: remove_offset + H * dk] + remove_bias.double()).reshape(-1, H, dk)
+            d = torch.exp(-decay_rate * torch.sigmoid(decay_in[rows].double() + decay_bias.double())).reshape(-1, H, dk)
+            u = k / torch.sqrt((k * k).sum(-1, keepdim=True) + unit_eps)
+            S = state[sg.state_slot].double()
+            for t in range(sg.n):
+                back = torch.einsum("hk,hkv->hv", u[t], S)
+                S = d[t][:, :, None] * S - (a[t] * u[t])[:, :, None] * back[:, None, :] + k[t][:, :, None] * v[t][:, None, :]
+                out[sg.row0 + t] = torch.einsum("hkv,hk->hv", S, r[t]).reshape(-1).float()
+            state[sg.state_slot] = S.float()
+
+    def rotate_kv_write(self, qkv, cos, sin, rotated, pairing, meta, cache, q_out, num_heads, num_kv_heads, key_dim, value_dim,
+                        q_norm=None, k_norm=None, norm_eps=0.0, query_temperature=None):
+        n, Hq, Hkv, dk, dv = qkv.shape[0], num_heads, num_kv_heads, key_dim, value_dim
+        pos, row = meta.pos.long(), meta.seq_row.long()
+        live = row >= 0
+        q = qkv[:, :Hq * dk].reshape(n, Hq, dk).float()
+        if q_norm is not None:
+            q = q * torch.rsqrt((q * q).mean(-1, keepdim=True) + norm_eps) * q_norm.float()
+        q = self._rot(q, cos, sin, rotated, pairing, pos)
+        if query_temperature is not None:
+            coef, every = query_temperature
+            q = q * (1 + coef * torch.log(torch.floor((pos.float() + 1) / every) + 1))[:, None, None]
+        q_out.copy_(torch.where(live[:, None, None], q, torch.zeros(())).reshape(n, -1).to(q_out.dtype))
+        if not cache.write:
+            return
+        k = qkv[:, Hq * dk: (Hq + Hkv) * dk].reshape(n, Hkv, dk).float()
+        if k_norm is not None:
+            k = k * torch.rsqrt((k * k).mean(-1, keepdim=True) + norm_eps) * k_norm.float()
+        k = self._rot(k, cos, sin, rotated, pairing, pos)
+        v = qkv[:, (Hq + Hkv) * dk: (Hq + Hkv) * dk + Hkv * dv].reshape(n, Hkv, dv)
+        table, bs = meta.table(cache.group), cache.page_size
+        for i in range(n):
+            if not live[i]:
+                continue
+            page = int(table[row[i], pos[i] // bs])
+            assert page >= 0, "a position has no page"
+            cache.keys[page, :, pos[i] % bs] = k[i].to(cache.keys.dtype)
+            cache.values[page, :, pos[i] % bs] = v[i].to(cache.values.dtype)
+
+    def sink_attention(self, q, cache, meta, out, num_heads, num_kv_heads, key_dim, value_dim, scale, window, keep_first, sink,
+                       softcap=0.0, gate=None):
+        n, Hq, Hkv, dk, dv = q.shape[0], num_heads, num_kv_heads, key_dim, value_dim
+        pos, row = meta.pos.long(), meta.seq_row.long()
+        table, bs = meta.table(cache.group), cache.page_size
+        out.zero_()
+        for i in range(n):
+            if row[i] < 0:
+                continue
+            p = int(pos[i])
+            js = [j for j in range(p + 1) if not window or p - j < window or j < keep_first]
+            pages = [int(table[row[i], j // bs]) for j in js]
+            assert min(pages) >= 0, "a visible key has no page"
+            K = torch.stack([cache.keys[pg, :, j % bs] for pg, j in zip(pages, js)]).float()
+            V = torch.stack([cache.values[pg, :, j % bs] for pg, j in zip(pages, js)]).float()
+            s = torch.einsum("gak,jgk->gaj", q[i].float().view(Hkv, Hq // Hkv, dk), K) * scale
+            if softcap:
+                s = softcap * torch.tanh(s / softcap)
+            if sink is not None:
+                s = torch.cat([s, sink.float().view(Hkv, Hq // Hkv, 1)], -1)
+            o = torch.einsum("gaj,jgv->gav", torch.softmax(s, -1)[..., :len(js)], V).reshape(Hq, dv)
+            if gate is not None:
+                g, off = gate
+                o = o * torch.sigmoid(g[i, off: off + Hq].float())[:, None]
+            out[i] = o.reshape(-1).to(out.dtype)
