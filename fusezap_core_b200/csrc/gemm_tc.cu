@@ -60,7 +60,12 @@ __device__ __forceinline__ float ld_dsmem(uint32_t addr, uint32_t rank) {
   asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote));
   return v;
 }
-__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + __expf(-g)) * u; }
+// The gated activation of the fused gate/up product. kind 1: silu(g) * u; 2: the tanh form of gelu,
+// 0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3))) * u.
+__device__ __forceinline__ float glu_mul(float g, float u, int kind) {
+  if (kind == 2) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+  return g / (1.0f + __expf(-g)) * u;
+}
 // (value, index) order of numpy.argmax: a NaN is the maximum, among equals the lower index wins; index 0x7fffffff: none
 __device__ __forceinline__ bool am_better(float v, int i, float bv, int bi) {
   if (i == 0x7fffffff) return false;
@@ -353,7 +358,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           __nv_bfloat16* dst = p.c_bf16 + (size_t)(tile_b * BN) * (p.feats >> 1) + tile_a * 64 + f;
 #pragma unroll 8
           for (int c = par; c < cols; c += 2)
-            dst[(size_t)c * (p.feats >> 1)] = __float2bfloat16_rn(silu_mul(tile[c * BM + f] + bg, tile[c * BM + f + 64] + bu));
+            dst[(size_t)c * (p.feats >> 1)] = __float2bfloat16_rn(glu_mul(tile[c * BM + f] + bg, tile[c * BM + f + 64] + bu, p.swiglu));
         }
         n_my = 0;
       }
@@ -408,7 +413,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const int half = p.feats >> 1;
             for (int i = 0; i < ni; ++i) {
               const int m = tile_b * BN + (int)rank + (i0 + i) * p.splits;
-              p.c_bf16[(size_t)m * half + tile_a * 64 + r] = __float2bfloat16_rn(silu_mul(ex[i * BM + r], ex[i * BM + r + 64]));
+              p.c_bf16[(size_t)m * half + tile_a * 64 + r] = __float2bfloat16_rn(glu_mul(ex[i * BM + r], ex[i * BM + r + 64], p.swiglu));
             }
           }
           asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -493,7 +498,7 @@ __device__ __forceinline__ void rows_store_tile(const Params& p, uint32_t taddr,
       for (int i = 0; i < 16; i += 2) {
         const float g0 = v[i] + (p.bias ? p.bias[n + i] : 0.f), g1 = v[i + 1] + (p.bias ? p.bias[n + i + 1] : 0.f);
         const float u0 = u[i] + (p.bias ? p.bias[n + 64 + i] : 0.f), u1 = u[i + 1] + (p.bias ? p.bias[n + 64 + i + 1] : 0.f);
-        const __nv_bfloat162 h2 = __floats2bfloat162_rn(silu_mul(g0, u0), silu_mul(g1, u1));
+        const __nv_bfloat162 h2 = __floats2bfloat162_rn(glu_mul(g0, u0, p.swiglu), glu_mul(g1, u1, p.swiglu));
         w[i >> 1] = *(const uint32_t*)&h2;
       }
       uint4* dst = (uint4*)(p.c_bf16 + (size_t)row * (p.feats >> 1) + (n >> 7) * 64 + (n & 63));
@@ -1376,12 +1381,13 @@ FZ_API int fz_gemm_tc_argmax(const void* x, const void* w, const float* bias, in
 
 // Fused gate/up product and SwiGLU: w is [2 I, K] with rows in blocks of 128 = [64 gate rows | 64 up rows] of the same 64
 // features (bias packed the same way, or null); out is bf16 [M, I] = silu(x . gate^T) * (x . up^T). I % 64 == 0.
+// kind 1: silu, 2: the tanh form of gelu.
 FZ_API int fz_gemm_tc_swiglu(const void* x, const void* w_packed, const float* bias_packed, void* out, int M, int I, int K,
-                             int* err, cudaStream_t stream) {
-  if (I <= 0 || I % 64) return FZ_BAD_SHAPE;
+                             int kind, int* err, cudaStream_t stream) {
+  if (I <= 0 || I % 64 || (kind != 1 && kind != 2)) return FZ_BAD_SHAPE;
   if (((uintptr_t)out) & 15) return FZ_BAD_ALIGNMENT;
   Params f{};
-  f.swiglu = 1;
+  f.swiglu = kind;
   return gemm_tc_impl(x, w_packed, bias_packed, out, FZ_BF16, M, 2 * I, K, f, err, stream);
 }
 

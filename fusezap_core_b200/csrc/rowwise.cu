@@ -400,8 +400,13 @@ FZ_API int fz_rope_kv_write(const float* qkv, const float* cos_t, const float* s
 }
 
 // ------------------------------------------------------------------------------------------------ SwiGLU
+// kind 1: silu(g); 2: the tanh form of gelu, 0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3))).
+__device__ __forceinline__ float gate_act(float g, int kind) {
+  if (kind == 2) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+  return g / (1.0f + expf(-g));
+}
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, long long total, int I) {
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, long long total, int I, int kind) {
   fz_grid_launch_dependents();
   fz_grid_wait();
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
@@ -410,13 +415,13 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, lon
     const int i = (int)(idx - n * I);
     const float g = Cvt<T>::to_f(gu[n * 2 * I + i]);
     const float u = Cvt<T>::to_f(gu[n * 2 * I + I + i]);
-    out[idx] = Cvt<T>::from_f(g / (1.0f + expf(-g)) * u);
+    out[idx] = Cvt<T>::from_f(gate_act(g, kind) * u);
   }
 }
 
 // 16 bytes of gate and of up per thread (8 bf16 or 4 float32); needs I a multiple of that count and aligned operands.
 template <typename T>
-__global__ void swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, long long groups, int I) {
+__global__ void swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, long long groups, int I, int kind) {
   fz_grid_launch_dependents();
   fz_grid_wait();
   constexpr int V = 16 / sizeof(T);
@@ -434,14 +439,14 @@ __global__ void swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ out,
 #pragma unroll
     for (int j = 0; j < V; ++j) {
       const float gf = Cvt<T>::to_f(g[j]);
-      o[j] = Cvt<T>::from_f(gf / (1.0f + expf(-gf)) * Cvt<T>::to_f(u[j]));
+      o[j] = Cvt<T>::from_f(gate_act(gf, kind) * Cvt<T>::to_f(u[j]));
     }
     *(uint4*)(out + n * I + i) = oq;
   }
 }
 
 template <typename T>
-static int launch_swiglu(const void* gu, void* out, int N, int I, cudaStream_t stream) {
+static int launch_swiglu(const void* gu, void* out, int N, int I, int kind, cudaStream_t stream) {
   constexpr int V = 16 / sizeof(T);
   const long long total = (long long)N * I;
   const int block = 256;
@@ -449,20 +454,21 @@ static int launch_swiglu(const void* gu, void* out, int N, int I, cudaStream_t s
     const long long groups = total / V;
     long long blocks = (groups + block - 1) / block;
     if (blocks > 148LL * 16) blocks = 148LL * 16;
-    fz_launch(swiglu_vec_kernel<T>, dim3((int)blocks), dim3(block), 0, stream, (const T*)gu, (T*)out, groups, I);
+    fz_launch(swiglu_vec_kernel<T>, dim3((int)blocks), dim3(block), 0, stream, (const T*)gu, (T*)out, groups, I, kind);
   } else {
     long long blocks = (total + block - 1) / block;
     if (blocks > 148LL * 32) blocks = 148LL * 32;
-    fz_launch(swiglu_kernel<T>, dim3((int)blocks), dim3(block), 0, stream, (const T*)gu, (T*)out, total, I);
+    fz_launch(swiglu_kernel<T>, dim3((int)blocks), dim3(block), 0, stream, (const T*)gu, (T*)out, total, I, kind);
   }
   FZ_LAUNCH_CHECK();
   return FZ_OK;
 }
 
-FZ_API int fz_swiglu(const void* gu, void* out, int dtype, int N, int I, cudaStream_t stream) {
+FZ_API int fz_swiglu(const void* gu, void* out, int dtype, int N, int I, int kind, cudaStream_t stream) {
   if ((long long)N * I <= 0) return FZ_OK;
-  if (dtype == FZ_F32) return launch_swiglu<float>(gu, out, N, I, stream);
-  if (dtype == FZ_BF16) return launch_swiglu<__nv_bfloat16>(gu, out, N, I, stream);
+  if (kind != 1 && kind != 2) return FZ_BAD_SHAPE;
+  if (dtype == FZ_F32) return launch_swiglu<float>(gu, out, N, I, kind, stream);
+  if (dtype == FZ_BF16) return launch_swiglu<__nv_bfloat16>(gu, out, N, I, kind, stream);
   return FZ_BAD_DTYPE;
 }
 

@@ -24,14 +24,37 @@ __device__ __forceinline__ float rotated_value(const float* __restrict__ x, int 
   return i == a ? o1 : o2;
 }
 
+// Element i of a head after its optional norm: x[i] * inv * w[i] (w null: x[i] as it is).
+__device__ __forceinline__ float normed_value(const float* __restrict__ x, int i, float inv, const float* __restrict__ w) {
+  return w != nullptr ? x[i] * inv * w[i] : x[i];
+}
+// `rotated_value` of a head that is normed first.
+__device__ __forceinline__ float rotated_normed_value(const float* __restrict__ x, int i, int rotated, int pairing,
+                                                      const float* __restrict__ cs, const float* __restrict__ sn, float inv,
+                                                      const float* __restrict__ w) {
+  if (i >= rotated) return normed_value(x, i, inv, w);
+  const int half = rotated >> 1;
+  int j, a, b;
+  if (pairing == 0) { j = i < half ? i : i - half; a = j; b = j + half; }
+  else { j = i >> 1; a = 2 * j; b = a + 1; }
+  float o1, o2;
+  fz_rope_pair(normed_value(x, a, inv, w), normed_value(x, b, inv, w), cs[j], sn[j], o1, o2);
+  return i == a ? o1 : o2;
+}
+
+// A row of qkv is ld floats: [q heads | k heads | v heads | ...]. qn_w / kn_w (dk values, or null): every q / k head is
+// divided by its root mean square (norm_eps inside the root) and multiplied by the weight before the rotation. qt_every > 0:
+// q is multiplied by 1 + qt_coef * ln(floor((p + 1) / qt_every) + 1) after it.
 template <typename T>
 __global__ void __launch_bounds__(256)
-rotate_kv_write_kernel(const float* __restrict__ qkv, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+rotate_kv_write_kernel(const float* __restrict__ qkv, int ld, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                        int rotated, int pairing, int max_pos, const int* __restrict__ pos, const int* __restrict__ seq_row,
                        const int* __restrict__ table, int mb, T* __restrict__ k_pool, T* __restrict__ v_pool,
                        long long page_stride, long long head_stride, long long tok_stride, int page_size, int n_pages,
-                       int write, T* __restrict__ q_out, int Hq, int Hkv, int dk, int dv, int* err) {
+                       int write, T* __restrict__ q_out, int Hq, int Hkv, int dk, int dv, const float* __restrict__ qn_w,
+                       const float* __restrict__ kn_w, float norm_eps, float qt_coef, int qt_every, int* err) {
   fz_grid_launch_dependents();
+  extern __shared__ __align__(16) float inv_rms[];      // [Hq + Hkv], used where a norm is asked for
   const int n = blockIdx.x;
   const int row = seq_row[n], p = pos[n];      // the step's metadata: written by the host before the step's first kernel
   fz_grid_wait();
@@ -41,8 +64,7 @@ rotate_kv_write_kernel(const float* __restrict__ qkv, const float* __restrict__ 
     for (int i = threadIdx.x; i < Hq * dk; i += blockDim.x) qrow[i] = Cvt<T>::from_f(0.f);
     return;
   }
-  const int width = (Hq + Hkv) * dk + Hkv * dv;
-  const float* in = qkv + (size_t)n * width;
+  const float* in = qkv + (size_t)n * ld;
   const int half = rotated >> 1;
   const float* cs = cos_t + (size_t)p * half;
   const float* sn = sin_t + (size_t)p * half;
@@ -51,11 +73,25 @@ rotate_kv_write_kernel(const float* __restrict__ qkv, const float* __restrict__ 
     page = table[(size_t)row * mb + p / page_size];
     if (page < 0 || page >= n_pages) { if (threadIdx.x == 0) atomicOr(err, FZ_ERR_NO_PAGE); page = -1; }
   }
+  const int heads = write ? Hq + Hkv : Hq;
+  if (qn_w != nullptr || kn_w != nullptr) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int h = warp; h < heads; h += blockDim.x >> 5) {
+      const float* x = in + (size_t)h * dk;
+      float ss = 0.f;
+      for (int i = lane; i < dk; i += 32) ss = fmaf(x[i], x[i], ss);
+      ss = warp_sum(ss);
+      if (lane == 0) inv_rms[h] = 1.0f / sqrtf(ss / (float)dk + norm_eps);
+    }
+    __syncthreads();
+  }
+  const float temp = qt_every > 0 ? 1.0f + qt_coef * logf((float)((p + 1) / qt_every) + 1.0f) : 1.0f;
   const long long at = (long long)page * page_stride + (long long)(p % page_size) * tok_stride;
-  for (int e = threadIdx.x; e < (Hq + Hkv) * dk; e += blockDim.x) {
+  for (int e = threadIdx.x; e < heads * dk; e += blockDim.x) {
     const int head = e / dk, i = e - head * dk;
-    const float v = rotated_value(in + (size_t)head * dk, i, rotated, pairing, cs, sn);
-    if (head < Hq) qrow[e] = Cvt<T>::from_f(v);
+    const float* w = head < Hq ? qn_w : kn_w;
+    const float v = rotated_normed_value(in + (size_t)head * dk, i, rotated, pairing, cs, sn, w != nullptr ? inv_rms[head] : 1.0f, w);
+    if (head < Hq) qrow[e] = Cvt<T>::from_f(qt_every > 0 ? v * temp : v);
     else if (page >= 0) k_pool[at + (long long)(head - Hq) * head_stride + i] = Cvt<T>::from_f(v);
   }
   if (page >= 0) {
@@ -94,6 +130,8 @@ struct AttnArgs {
   int N;                                           // rows of the step
   int rows_per_block;                              // tile kernel: rows of a portion per block
   int unit_chunks, max_units; float* part;         // unit kernel: chunks per run, runs per row, (m, l, acc[dv]) per (row, head, run)
+  float softcap;                                   // > 0: the scaled score s becomes softcap * tanh(s / softcap)
+  const float* gate; int gate_ld, gate_off;        // not null: head h's result is multiplied by sigmoid(gate[n gate_ld + gate_off + h])
 };
 
 // The chunks a row at position p walks: `first_end + 1` chunks of kept tokens, then chunks c2 .. p / CHUNK.
@@ -132,14 +170,16 @@ __device__ __forceinline__ void load_chunk(const AttnArgs& a, const int* trow, i
 // One warp, one pair, one chunk: the online-softmax update. A chunk without a visible key changes nothing.
 template <int DPL>
 __device__ __forceinline__ void pair_chunk(const float* qh, const float* Ks, const float* Vs, int c, int p, int lo,
-                                           int keep_first, float scale, int dk, int dv, float& m, float& l, float* acc) {
+                                           int keep_first, float scale, float softcap, int dk, int dv, float& m, float& l, float* acc) {
   const int lane = threadIdx.x & 31;
   const int key = c * CHUNK + lane;
   const bool valid = key <= p && (key >= lo || key < keep_first);
   const float* kr = Ks + lane * (dk + 1);
   float s = 0.f;
   for (int d = 0; d < dk; ++d) s = fmaf(qh[d], kr[d], s);
-  s = valid ? s * scale : -INFINITY;
+  s *= scale;
+  if (softcap > 0.f) s = softcap * tanhf(s / softcap);
+  s = valid ? s : -INFINITY;
   const float mn = fmaxf(m, warp_max(s));
   if (mn == -INFINITY) return;                     // nothing seen so far, nothing here
   const float pj = valid ? expf(s - mn) : 0.f;
@@ -169,7 +209,8 @@ __device__ __forceinline__ void pair_finish(const AttnArgs& a, int n, int head, 
     corr = expf(m - mn);
     l = l * corr + expf(sk - mn);
   }
-  const float inv = 1.0f / l;
+  float inv = 1.0f / l;
+  if (a.gate != nullptr) inv *= 1.0f / (1.0f + expf(-a.gate[(size_t)n * a.gate_ld + a.gate_off + head]));
   T* o = (T*)a.out + ((size_t)n * a.Hq + head) * a.dv;
 #pragma unroll
   for (int i = 0; i < DPL; ++i) {
@@ -235,7 +276,7 @@ sink_attention_tile_kernel(const AttnArgs a) {
       if (pr >= pairs) break;
       const int p = p_first + pr / G;
       const int lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
-      pair_chunk<DPL>(Qs + pr * dk, Ks, Vs, c, p, lo, a.keep_first, a.scale, dk, dv, m[x], l[x], acc[x]);
+      pair_chunk<DPL>(Qs + pr * dk, Ks, Vs, c, p, lo, a.keep_first, a.scale, a.softcap, dk, dv, m[x], l[x], acc[x]);
     }
   }
 #pragma unroll
@@ -290,7 +331,7 @@ sink_attention_unit_kernel(const AttnArgs a) {
     for (int x = 0; x < MAX_PPW; ++x) {
       const int g = warp + x * ATT_WARPS;
       if (g >= G) break;
-      pair_chunk<DPL>(Qs + g * dk, Ks, Vs, c, p, walk.lo, a.keep_first, a.scale, dk, dv, m[x], l[x], acc[x]);
+      pair_chunk<DPL>(Qs + g * dk, Ks, Vs, c, p, walk.lo, a.keep_first, a.scale, a.softcap, dk, dv, m[x], l[x], acc[x]);
     }
   }
 #pragma unroll
@@ -699,10 +740,159 @@ gated_delta_scan_kernel(const T* __restrict__ qkv, int H, int Hk, int dk, int dv
   store_state(sp + 2 * (size_t)dkp, dkp, has[2], has[3], S[1]);
 }
 
+// S = diag(d) S - (a u)(u^T S) + k v^T, both products from the state before the token; o = S^T r. proj rows (ld floats):
+// [r (H dk) | k (H dk) | v (H dv) | ...], the removal inputs (H dk) from column off_a on; din (N, H dk): the decay inputs.
+// u = k / sqrt(sum k^2 + unit_eps), d = exp(-rate * sigmoid(din + dbias)), a = sigmoid(ain + abias), per key channel.
+template <int R>
+__global__ void __launch_bounds__(SCAN_MAX_THREADS)
+general_delta_scan_kernel(const float* __restrict__ proj, int ld, int H, int dk, int dv, int off_a, int tch,
+                          const float* __restrict__ din, const float* __restrict__ dbias, const float* __restrict__ abias,
+                          float rate, float unit_eps, float* __restrict__ state, const int* __restrict__ seg,
+                          float* __restrict__ out) {
+  fz_grid_launch_dependents();
+  const int s = blockIdx.x, h = blockIdx.y;
+  const int row0 = seg[4 * s], cnt = seg[4 * s + 1], slot = seg[4 * s + 3];
+  fz_grid_wait();
+  if (cnt <= 0 || slot < 0) return;
+  extern __shared__ __align__(16) float smem[];
+  const int NT = blockDim.x;
+  const int dkp = R * DPT, COLS = NT / R * DC;
+  float* rs = smem;                    // [tch][dkp]   what the recurrence reads: r
+  float* ks = rs + tch * dkp;          //              k
+  float* us = ks + tch * dkp;          //              the unit key
+  float* ds = us + tch * dkp;          //              the decay
+  float* ns = ds + tch * dkp;          //              -(a * u)
+  float* vs = ns + tch * dkp;          // [tch][COLS]
+  float* rr = vs + tch * COLS;         // [tch][dk]    raw: as the projections left them
+  float* rk = rr + tch * dk;
+  float* ra = rk + tch * dk;           //              removal inputs
+  float* rd = ra + tch * dk;           //              decay inputs
+  float* rv = rd + tch * dk;           // [tch][COLS]
+  int group, r;
+  scan_place<R>(group, r);
+  const int col0 = blockIdx.z * COLS, col = col0 + group * DC;      // this thread's first column
+  const int ncols = min(COLS, dv - col0);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* sp = state + (((size_t)slot * H + h) * dv + col) * dkp + r * DPT;
+  const bool has[DC] = {col < dv, col + 1 < dv, col + 2 < dv, col + 3 < dv};
+  float2 S[DC / 2][DPT];
+  load_state(sp, dkp, has[0], has[1], S[0]);
+  load_state(sp + 2 * (size_t)dkp, dkp, has[2], has[3], S[1]);
+  // copies of 16 bytes where every run starts on a 16-byte boundary and has a length that is a multiple of four
+  const int vec = ((dk | ld | dv | ncols | off_a | (H * dk)) & 3) == 0 && aligned16(proj) && aligned16(din) ? 4 : 1;
+  const int uq = dk / vec, uv = ncols / vec;
+  const int per_token = 4 * uq + uv;
+  auto issue = [&](int t0) {
+    const int tc = min(tch, cnt - t0);
+    for (int e = threadIdx.x; e < tc * per_token; e += NT) {
+      const int tt = e / per_token;
+      int i = e - tt * per_token;
+      const size_t n = (size_t)(row0 + t0 + tt);
+      const float* in = proj + n * ld;
+      if (i < uq) { cp_words(rr + tt * dk, in + (size_t)h * dk, i, vec); continue; }
+      i -= uq;
+      if (i < uq) { cp_words(rk + tt * dk, in + (size_t)(H + h) * dk, i, vec); continue; }
+      i -= uq;
+      if (i < uq) { cp_words(ra + tt * dk, in + off_a + (size_t)h * dk, i, vec); continue; }
+      i -= uq;
+      if (i < uq) { cp_words(rd + tt * dk, din + n * H * dk + (size_t)h * dk, i, vec); continue; }
+      i -= uq;
+      cp_words(rv + tt * COLS, in + (size_t)2 * H * dk + (size_t)h * dv + col0, i, vec);
+    }
+    cp_async_commit();
+  };
+  auto cook = [&](int t0) {
+    const int tc = min(tch, cnt - t0);
+    for (int tt = warp; tt < tc; tt += NT / 32) {      // a warp cooks a token: the unit key, the decay, the removal rate
+      const float* kin = rk + tt * dk;
+      float sk = 0.f;
+      for (int i = lane; i < dk; i += 32) sk = fmaf(kin[i], kin[i], sk);
+      const float nk = sqrtf(warp_sum(sk) + unit_eps);
+      for (int i = lane; i < dkp; i += 32) {
+        float rv_ = 0.f, kv = 0.f, uv_ = 0.f, dv_ = 0.f, nv = 0.f;
+        if (i < dk) {
+          rv_ = rr[tt * dk + i];
+          kv = kin[i];
+          uv_ = __fdiv_rn(kv, nk);
+          const float zd = rd[tt * dk + i] + dbias[(size_t)h * dk + i];
+          dv_ = expf(-rate * (1.0f / (1.0f + expf(-zd))));
+          const float za = ra[tt * dk + i] + abias[(size_t)h * dk + i];
+          nv = -(uv_ * (1.0f / (1.0f + expf(-za))));
+        }
+        rs[tt * dkp + i] = rv_;
+        ks[tt * dkp + i] = kv;
+        us[tt * dkp + i] = uv_;
+        ds[tt * dkp + i] = dv_;
+        ns[tt * dkp + i] = nv;
+      }
+    }
+    for (int e = threadIdx.x; e < tc * COLS; e += NT) {
+      const int c = e % COLS;
+      vs[e] = c < ncols ? rv[e] : 0.f;
+    }
+  };
+
+  issue(0);
+  cp_async_wait();
+  __syncthreads();
+  cook(0);
+  __syncthreads();
+  for (int t0 = 0; t0 < cnt; t0 += tch) {
+    const int tc = min(tch, cnt - t0);
+    const bool more = t0 + tch < cnt;
+    if (more) issue(t0 + tch);
+    float* dst = out + (size_t)(row0 + t0) * H * dv + (size_t)h * dv + col;
+#pragma unroll 2
+    for (int tt = 0; tt < tc; ++tt, dst += (size_t)H * dv) {
+      const float4 v4 = *(const float4*)(vs + tt * COLS + group * DC);
+      const float2 v[DC / 2] = {make_float2(v4.x, v4.y), make_float2(v4.z, v4.w)};
+      float kk[DPT], qq[DPT], uu[DPT], dd[DPT], nn[DPT];
+      load8(us + tt * dkp + r * DPT, uu);
+      float2 back[DC / 2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+#pragma unroll
+      for (int i = 0; i < DPT; ++i) {
+        const float2 u2 = both(uu[i]);
+#pragma unroll
+        for (int j = 0; j < DC / 2; ++j) back[j] = __ffma2_rn(S[j][i], u2, back[j]);
+      }
+      const float2 b[DC / 2] = {make_float2(lanes_sum<R>(back[0].x), lanes_sum<R>(back[0].y)),
+                                make_float2(lanes_sum<R>(back[1].x), lanes_sum<R>(back[1].y))};
+      load8(ks + tt * dkp + r * DPT, kk);
+      load8(rs + tt * dkp + r * DPT, qq);
+      load8(ds + tt * dkp + r * DPT, dd);
+      load8(ns + tt * dkp + r * DPT, nn);
+      float2 o[DC / 2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+#pragma unroll
+      for (int i = 0; i < DPT; ++i) {
+        const float2 k2 = both(kk[i]), q2 = both(qq[i]), d2 = both(dd[i]), n2 = both(nn[i]);
+#pragma unroll
+        for (int j = 0; j < DC / 2; ++j) {
+          S[j][i] = __ffma2_rn(d2, S[j][i], __ffma2_rn(k2, v[j], __fmul2_rn(n2, b[j])));
+          o[j] = __ffma2_rn(S[j][i], q2, o[j]);
+        }
+      }
+      const float res[DC] = {lanes_sum<R>(o[0].x), lanes_sum<R>(o[0].y), lanes_sum<R>(o[1].x), lanes_sum<R>(o[1].y)};
+      if (r == 0) {
+#pragma unroll
+        for (int j = 0; j < DC; ++j)
+          if (has[j]) dst[j] = res[j];
+      }
+    }
+    if (more) {
+      cp_async_wait();
+      __syncthreads();
+      cook(t0 + tch);
+      __syncthreads();
+    }
+  }
+  store_state(sp, dkp, has[0], has[1], S[0]);
+  store_state(sp + 2 * (size_t)dkp, dkp, has[2], has[3], S[1]);
+}
+
 // out[n, h, c] = o / sqrt(mean_c o^2 + eps) * w[c] * act(gate[n, goff + h dv + c]); a warp per (row, head).
 template <typename TO>
 __global__ void __launch_bounds__(256)
-head_norm_gate_kernel(const float* __restrict__ o, int H, int dv, const float* __restrict__ w, float eps,
+head_norm_gate_kernel(const float* __restrict__ o, int H, int dv, const float* __restrict__ w, int w_per_head, float eps,
                       const float* __restrict__ gate, int ldg, int goff, int act, const int* __restrict__ seq_row,
                       TO* __restrict__ out) {
   fz_grid_launch_dependents();
@@ -722,7 +912,7 @@ head_norm_gate_kernel(const float* __restrict__ o, int H, int dv, const float* _
     const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)dv + eps);
     for (int c = lane; c < dv; c += 32) {
       float v = x[c] * inv;
-      if (w != nullptr) v *= w[c];
+      if (w != nullptr) v *= w[w_per_head ? h * dv + c : c];
       if (gate != nullptr) {
         const float z = gate[(size_t)n * ldg + goff + (size_t)h * dv + c];
         const float sg = 1.0f / (1.0f + expf(-z));
@@ -903,21 +1093,26 @@ int dispatch_sink(const AttnArgs& a, int N, int n_seg, int max_portion, int unit
 }
 }  // namespace
 
-FZ_API int fz_rotate_kv_write(const float* qkv, const float* cos_t, const float* sin_t, int rotated, int pairing, int max_pos,
+FZ_API int fz_rotate_kv_write(const float* qkv, int ld, const float* cos_t, const float* sin_t, int rotated, int pairing, int max_pos,
                               const int* pos, const int* seq_row, const int* table, int mb, void* k_pool, void* v_pool,
                               long long page_stride, long long head_stride, long long tok_stride, int page_size,
-                              int n_pages, int write, void* q_out, int dtype, int N, int Hq, int Hkv, int dk, int dv, int* err,
+                              int n_pages, int write, void* q_out, int dtype, int N, int Hq, int Hkv, int dk, int dv,
+                              const float* qn_w, const float* kn_w, float norm_eps, float qt_coef, int qt_every, int* err,
                               cudaStream_t stream) {
   if (N <= 0) return FZ_OK;
-  if (rotated < 0 || rotated > dk || (rotated & 1) || page_size <= 0 || Hq <= 0 || Hkv <= 0 || dk <= 0 || dv <= 0) return FZ_BAD_SHAPE;
+  if (rotated < 0 || rotated > dk || (rotated & 1) || page_size <= 0 || Hq <= 0 || Hkv <= 0 || dk <= 0 || dv <= 0 ||
+      ld < (write ? (Hq + Hkv) * dk + Hkv * dv : Hq * dk) || qt_every < 0 || (write && (qn_w == nullptr) != (kn_w == nullptr)))
+    return FZ_BAD_SHAPE;
+  const size_t smem = sizeof(float) * (size_t)(Hq + Hkv);
+  if (smem > 48 * 1024) return FZ_BAD_SHAPE;
   if (dtype == FZ_F32)
-    fz_launch(rotate_kv_write_kernel<float>, dim3(N), dim3(256), 0, stream, qkv, cos_t, sin_t, rotated, pairing, max_pos, pos,
+    fz_launch(rotate_kv_write_kernel<float>, dim3(N), dim3(256), smem, stream, qkv, ld, cos_t, sin_t, rotated, pairing, max_pos, pos,
               seq_row, table, mb, (float*)k_pool, (float*)v_pool, page_stride, head_stride, tok_stride, page_size, n_pages,
-              write, (float*)q_out, Hq, Hkv, dk, dv, err);
+              write, (float*)q_out, Hq, Hkv, dk, dv, qn_w, kn_w, norm_eps, qt_coef, qt_every, err);
   else if (dtype == FZ_BF16)
-    fz_launch(rotate_kv_write_kernel<__nv_bfloat16>, dim3(N), dim3(256), 0, stream, qkv, cos_t, sin_t, rotated, pairing, max_pos,
+    fz_launch(rotate_kv_write_kernel<__nv_bfloat16>, dim3(N), dim3(256), smem, stream, qkv, ld, cos_t, sin_t, rotated, pairing, max_pos,
               pos, seq_row, table, mb, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, page_stride, head_stride, tok_stride,
-              page_size, n_pages, write, (__nv_bfloat16*)q_out, Hq, Hkv, dk, dv, err);
+              page_size, n_pages, write, (__nv_bfloat16*)q_out, Hq, Hkv, dk, dv, qn_w, kn_w, norm_eps, qt_coef, qt_every, err);
   else return FZ_BAD_DTYPE;
   FZ_LAUNCH_CHECK();
   return FZ_OK;
@@ -943,12 +1138,14 @@ FZ_API int fz_sink_attention(const void* q, const void* k_pool, const void* v_po
                              const int* seg, int n_seg, int max_portion, const int* table, int mb, long long page_stride,
                              long long head_stride, long long tok_stride, int page_size, int n_pages, void* out, int dtype,
                              int N, int Hq, int Hkv, int dk, int dv, float scale, int window, int keep_first,
-                             const float* sink, int unit_chunks, int units, float* part, int* err, cudaStream_t stream) {
+                             const float* sink, int unit_chunks, int units, float* part, float softcap, const float* gate,
+                             int gate_ld, int gate_off, int* err, cudaStream_t stream) {
   if (N <= 0 || n_seg <= 0) return FZ_OK;
+  if (softcap < 0.f || (gate != nullptr && (gate_off < 0 || gate_off + Hq > gate_ld))) return FZ_BAD_SHAPE;
   if (fz_sink_attention_check(Hq, Hkv, dk, dv) != FZ_OK || page_size <= 0 || window < 0 || keep_first < 0 || max_portion <= 0 ||
       (units > 0 && (unit_chunks <= 0 || part == nullptr || units > 65535))) return FZ_BAD_SHAPE;
   AttnArgs a = {q, k_pool, v_pool, pos, seq_row, seg, table, mb, page_stride, head_stride, tok_stride, page_size, n_pages, out,
-                Hq, Hkv, dk, dv, scale, window, keep_first, sink, err, N, 1, unit_chunks, units, part};
+                Hq, Hkv, dk, dv, scale, window, keep_first, sink, err, N, 1, unit_chunks, units, part, softcap, gate, gate_ld, gate_off};
   if (dtype == FZ_F32) return dispatch_sink<float>(a, N, n_seg, max_portion, units, stream);
   if (dtype == FZ_BF16) return dispatch_sink<__nv_bfloat16>(a, N, n_seg, max_portion, units, stream);
   return FZ_BAD_DTYPE;
@@ -1041,16 +1238,49 @@ FZ_API int fz_gated_delta_scan(const void* qkv, int dtype, int H, int Hk, int dk
   return FZ_BAD_DTYPE;
 }
 
+static size_t general_delta_smem(int dk, int R, int cols, int tch) {
+  const int dkp = R * DPT;
+  return sizeof(float) * (size_t)tch * ((size_t)5 * dkp + cols + 4 * dk + cols);
+}
+
+template <int R>
+static int launch_general_delta(const float* proj, int ld, int H, int dk, int dv, int off_a, const float* din, const float* dbias,
+                                const float* abias, float rate, float unit_eps, float* state, const int* seg, int n_seg,
+                                float* out, cudaStream_t stream) {
+  const int threads = scan_threads(dv, R), cols = threads / R * DC;
+  const int tch = general_delta_smem(dk, R, cols, 16) <= 48 * 1024 ? 16 : 8;
+  const size_t smem = general_delta_smem(dk, R, cols, tch);
+  static size_t allowed = 48 * 1024;
+  int st = allow_smem(general_delta_scan_kernel<R>, smem, allowed);
+  if (st != FZ_OK) return st;
+  fz_launch(general_delta_scan_kernel<R>, dim3(n_seg, H, (dv + cols - 1) / cols), dim3(threads), smem, stream, proj, ld, H, dk,
+            dv, off_a, tch, din, dbias, abias, rate, unit_eps, state, seg, out);
+  FZ_LAUNCH_CHECK();
+  return FZ_OK;
+}
+
+FZ_API int fz_general_delta_scan(const float* proj, int ld, int H, int dk, int dv, int off_a, const float* din,
+                                 const float* dbias, const float* abias, float rate, float unit_eps, float* state,
+                                 const int* seg, int n_seg, float* out, cudaStream_t stream) {
+  if (n_seg <= 0) return FZ_OK;
+  if (H <= 0 || H > 65535 || dv <= 0 || fz_recurrent_key_pad(dk) < 0 || ld < 2 * H * dk + H * dv || off_a < 0 || off_a + H * dk > ld)
+    return FZ_BAD_SHAPE;
+#define FZ_CALL(R) launch_general_delta<R>(proj, ld, H, dk, dv, off_a, din, dbias, abias, rate, unit_eps, state, seg, n_seg, out, stream)
+  FZ_BY_LANES(lanes_per_column(dk), FZ_CALL)
+#undef FZ_CALL
+}
+
 // act: 0 none, 1 sigmoid, 2 silu.
-FZ_API int fz_head_norm_gate(const float* o, int N, int H, int dv, const float* w, float eps, const float* gate, int ldg,
+// w: dv values shared by the heads, or (w_per_head) H * dv values.
+FZ_API int fz_head_norm_gate(const float* o, int N, int H, int dv, const float* w, int w_per_head, float eps, const float* gate, int ldg,
                              int goff, int act, const int* seq_row, void* out, int out_dtype, cudaStream_t stream) {
   if (N <= 0) return FZ_OK;
   if (H <= 0 || dv <= 0) return FZ_BAD_SHAPE;
   const int W = H < 8 ? H : 8;
   if (out_dtype == FZ_F32)
-    fz_launch(head_norm_gate_kernel<float>, dim3(N), dim3(32 * W), 0, stream, o, H, dv, w, eps, gate, ldg, goff, act, seq_row, (float*)out);
+    fz_launch(head_norm_gate_kernel<float>, dim3(N), dim3(32 * W), 0, stream, o, H, dv, w, w_per_head, eps, gate, ldg, goff, act, seq_row, (float*)out);
   else if (out_dtype == FZ_BF16)
-    fz_launch(head_norm_gate_kernel<__nv_bfloat16>, dim3(N), dim3(32 * W), 0, stream, o, H, dv, w, eps, gate, ldg, goff, act, seq_row, (__nv_bfloat16*)out);
+    fz_launch(head_norm_gate_kernel<__nv_bfloat16>, dim3(N), dim3(32 * W), 0, stream, o, H, dv, w, w_per_head, eps, gate, ldg, goff, act, seq_row, (__nv_bfloat16*)out);
   else return FZ_BAD_DTYPE;
   FZ_LAUNCH_CHECK();
   return FZ_OK;

@@ -1,0 +1,126 @@
+// Row kernels of depth-averaged layers and of the hashed pair embedding, and a columnwise activation. All arithmetic is
+// 32-bit; T is the dtype of a table that is read or of an activation that is written.
+#include "common.cuh"
+#include <math.h>
+
+namespace {
+// x[n] += table[r], r chosen by a hash of (previous token, token). One block per row. The block of a portion's first row
+// reads the request's previous token from its state slot and then leaves the portion's last token there (no other block
+// touches that slot: a request has one portion in a step).
+template <typename T>
+__global__ void __launch_bounds__(256)
+hashed_pair_embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, const int* __restrict__ seq_row,
+                         const int* __restrict__ seg, int* __restrict__ state, int buckets, long long mul_prev,
+                         long long mul_cur, int vocab, float* __restrict__ x, int D, int* err) {
+  fz_grid_launch_dependents();
+  const int n = blockIdx.x;
+  const int row = seq_row[n];
+  fz_grid_wait();
+  if (row < 0) return;
+  const int row0 = seg[4 * row], cnt = seg[4 * row + 1], pos0 = seg[4 * row + 2], slot = seg[4 * row + 3];
+  const int i = n - row0;
+  __shared__ int prev_s;
+  if (threadIdx.x == 0) {
+    int prev = 0;
+    if (i > 0) prev = ids[n - 1];
+    else if (slot >= 0) {
+      prev = state[slot];
+      state[slot] = ids[row0 + cnt - 1];
+    }
+    prev_s = prev;
+  }
+  __syncthreads();
+  const int tok = ids[n], prev = prev_s;
+  if (tok < 0 || tok >= vocab || prev < 0 || prev >= vocab) { if (threadIdx.x == 0) atomicOr(err, FZ_ERR_TOKEN_RANGE); return; }
+  const long long r = pos0 + i == 0 ? (long long)buckets : ((long long)prev * mul_prev + (long long)tok * mul_cur) % buckets;
+  const T* src = table + (size_t)r * D;
+  float* dst = x + (size_t)n * D;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) dst[d] += Cvt<T>::to_f(src[d]);
+}
+
+// streams: (N, L1, D). X = x + delta; streams[n, depth + 1] = X; x = sum_j coef[j] streams[n, j], j = 0 .. depth + 1, by
+// fused multiply-adds in rising j from zero. coef null (depth -1): only X is kept and x = X.
+__global__ void __launch_bounds__(256)
+depth_average_kernel(float* __restrict__ streams, int L1, int depth, const float* __restrict__ coef, float* __restrict__ x,
+                     const float* __restrict__ delta, int D) {
+  fz_grid_launch_dependents();
+  fz_grid_wait();
+  const int n = blockIdx.x;
+  float* st = streams + (size_t)n * L1 * D;
+  float* xr = x + (size_t)n * D;
+  const float* dr = delta != nullptr ? delta + (size_t)n * D : nullptr;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    const float X = dr != nullptr ? xr[d] + dr[d] : xr[d];
+    st[(size_t)(depth + 1) * D + d] = X;
+    float acc = X;
+    if (coef != nullptr) {
+      acc = 0.f;
+      for (int j = 0; j <= depth; ++j) acc = fmaf(coef[j], st[(size_t)j * D + d], acc);
+      acc = fmaf(coef[depth + 1], X, acc);
+    }
+    xr[d] = acc;
+  }
+}
+
+// out[n, j] = act(src[n, off + j]). kind 0: tanh, 1: sigmoid, 2: silu, 3: the tanh form of gelu.
+template <typename T>
+__global__ void __launch_bounds__(256)
+activate_kernel(const float* __restrict__ src, int ld, int off, int kind, T* __restrict__ out, int W, long long total) {
+  fz_grid_launch_dependents();
+  fz_grid_wait();
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+    const long long n = idx / W;
+    const int j = (int)(idx - n * W);
+    const float z = src[n * ld + off + j];
+    float v;
+    if (kind == 0) v = tanhf(z);
+    else if (kind == 1) v = 1.0f / (1.0f + expf(-z));
+    else if (kind == 2) v = z / (1.0f + expf(-z));
+    else v = 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    out[idx] = Cvt<T>::from_f(v);
+  }
+}
+}  // namespace
+
+FZ_API int fz_hashed_pair_embed(const void* table, int dtype, const int* ids, const int* seq_row, const int* seg, int* state,
+                                int buckets, long long mul_prev, long long mul_cur, int vocab, float* x, int N, int D, int* err,
+                                cudaStream_t stream) {
+  if (N <= 0 || D <= 0) return FZ_OK;
+  if (buckets <= 0 || mul_prev < 0 || mul_cur < 0) return FZ_BAD_SHAPE;
+  if (dtype == FZ_F32)
+    fz_launch(hashed_pair_embed_kernel<float>, dim3(N), dim3(256), 0, stream, (const float*)table, ids, seq_row, seg, state,
+              buckets, mul_prev, mul_cur, vocab, x, D, err);
+  else if (dtype == FZ_BF16)
+    fz_launch(hashed_pair_embed_kernel<__nv_bfloat16>, dim3(N), dim3(256), 0, stream, (const __nv_bfloat16*)table, ids, seq_row,
+              seg, state, buckets, mul_prev, mul_cur, vocab, x, D, err);
+  else return FZ_BAD_DTYPE;
+  FZ_LAUNCH_CHECK();
+  return FZ_OK;
+}
+
+FZ_API int fz_depth_average(float* streams, int L1, int depth, const float* coef, float* x, const float* delta, int N, int D,
+                            cudaStream_t stream) {
+  if (N <= 0 || D <= 0) return FZ_OK;
+  if (depth < -1 || depth + 1 >= L1 || (coef == nullptr) != (depth == -1)) return FZ_BAD_SHAPE;
+  fz_launch(depth_average_kernel, dim3(N), dim3(256), 0, stream, streams, L1, depth, coef, x, delta, D);
+  FZ_LAUNCH_CHECK();
+  return FZ_OK;
+}
+
+FZ_API int fz_activate(const float* src, int ld, int off, int kind, void* out, int dtype, int N, int W, cudaStream_t stream) {
+  const long long total = (long long)N * W;
+  if (total <= 0) return FZ_OK;
+  if (kind < 0 || kind > 3 || off < 0 || off + W > ld) return FZ_BAD_SHAPE;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148LL * 16) blocks = 148LL * 16;
+  if (dtype == FZ_F32) fz_launch(activate_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, src, ld, off, kind, (float*)out, W, total);
+  else if (dtype == FZ_BF16)
+    fz_launch(activate_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(256), 0, stream, src, ld, off, kind, (__nv_bfloat16*)out, W, total);
+  else return FZ_BAD_DTYPE;
+  FZ_LAUNCH_CHECK();
+  return FZ_OK;
+}
+
+#ifdef FZ_TIMELINE
+FZ_TIMELINE_READER(stream_rows)
+#endif

@@ -30,6 +30,8 @@ LIBRARIES: dict[str, list[str]] = {
     "fzb200_latent_tc": ["attn_latent_tc.cu"],                               # bfloat16 only: the same on tensor cores
     # recurrent mixers, attention with a window, kept first tokens and a sink, the routed experts' router (both dtypes)
     "fzb200_seq": ["seq_mix.cu"],
+    # depth-averaged layers, the hashed pair embedding, a columnwise activation (both dtypes)
+    "fzb200_rows": ["stream_rows.cu"],
     "fzb200_seq_tc": ["attn_sink_mma.cu"],                                   # bfloat16 only: that attention on tensor cores
     "fzb200_tc": ["gemm_tc.cu"],                                             # bfloat16 only: tcgen05 / TMA products
     # bfloat16 only: attention over separate keys and values per kv head (tcgen05 / TMA / mma.sync); built when a model

@@ -121,7 +121,7 @@ class CudaOps(Ops):
         if self.dtype == torch.bfloat16:
             self.tc = load("fzb200_tc")      # tcgen05 / TMA kernels
         self.use_tensor_cores = self.tc is not None
-        self._attn_tc = self._mix = self._mix_tc = self._latent = self._latent_tc = self._seq = self._seq_tc = None   # libraries loaded (and built) when a part first asks for their kernels
+        self._attn_tc = self._mix = self._mix_tc = self._latent = self._latent_tc = self._seq = self._seq_tc = self._rows = None   # libraries loaded (and built) when a part first asks for their kernels
         self.prefill_tcgen05 = True        # False: long portions on the mma.sync flash-attention kernel
         self.fuse_swiglu = True            # gate/up product and SwiGLU in one kernel where the sizes allow it
         self.fuse_argmax = True            # lm_head product and argmax in one pass where no logits are asked for
@@ -184,6 +184,13 @@ class CudaOps(Ops):
         if self._seq is None:
             self._seq = load("fzb200_seq")
         return self._seq
+
+    @property
+    def rows(self):
+        """Depth-averaged layers, the hashed pair embedding, a columnwise activation."""
+        if self._rows is None:
+            self._rows = load("fzb200_rows")
+        return self._rows
 
     @property
     def mix(self):
@@ -399,14 +406,15 @@ class CudaOps(Ops):
             b = torch.stack([gate_bias.float().view(i // 64, 64), up_bias.float().view(i // 64, 64)], 1).reshape(2 * i).contiguous()
         return (w, b, i)
 
-    def linear_swiglu(self, a, packed, out) -> None:
+    def linear_swiglu(self, a, packed, out, activation: str = "silu") -> None:
         w, b, i = packed
         self._want(a, "linear input", (torch.bfloat16,), 2)
         self._want(out, "swiglu output", (torch.bfloat16,), 2)
         m, k = a.shape
         if w.shape != (2 * i, k) or out.shape != (m, i):
             raise KernelError(f"linear_swiglu: a {tuple(a.shape)}, packed {tuple(w.shape)}, out {tuple(out.shape)}")
-        self._check(self.tc.fz_gemm_tc_swiglu(_p(a), _p(w), _p(b), _p(out), c_int(m), c_int(i), c_int(k), _p(self.err),
+        self._check(self.tc.fz_gemm_tc_swiglu(_p(a), _p(w), _p(b), _p(out), c_int(m), c_int(i), c_int(k),
+                                              c_int(self._gate_kind(activation)), _p(self.err),
                                               self._stream()), "linear_swiglu (tensor cores)",
                     ideal_linear_bytes(m, 2 * i, k, 2, 2, 1))
 
@@ -557,13 +565,20 @@ class CudaOps(Ops):
             c_longlong(page_stride), c_int(cache.page_size), _p(out), c_int(_CODE[self.dtype]), c_int(n), c_int(hq),
             c_int(hkv), c_int(hd), c_float(scale), c_int(window), _p(self.err), self._stream()), "paged_attention", kv)
 
-    def swiglu(self, gate_up, out) -> None:
+    @staticmethod
+    def _gate_kind(activation: str) -> int:
+        kind = {"silu": 1, "gelu_tanh": 2}.get(activation)
+        if kind is None:
+            raise KernelError(f"gate activation {activation!r} is not one of 'silu', 'gelu_tanh'")
+        return kind
+
+    def swiglu(self, gate_up, out, activation: str = "silu") -> None:
         self._want(gate_up, "gate_up", (self.dtype,), 2)
         self._want(out, "swiglu output", (self.dtype,), 2)
         n, i = out.shape
         if gate_up.shape != (n, 2 * i):
             raise KernelError(f"swiglu: gate_up {tuple(gate_up.shape)}, out {tuple(out.shape)}")
-        self._check(self.core.fz_swiglu(_p(gate_up), _p(out), c_int(_CODE[self.dtype]), c_int(n), c_int(i),
+        self._check(self.core.fz_swiglu(_p(gate_up), _p(out), c_int(_CODE[self.dtype]), c_int(n), c_int(i), c_int(self._gate_kind(activation)),
                                         self._stream()), "swiglu")
 
     def argmax(self, logits, out) -> None:
@@ -904,8 +919,8 @@ class CudaOps(Ops):
             raise KernelError(f"head_norm_gate: o {tuple(o.shape)}, out {tuple(out.shape)}, {heads} heads of {value_dim}")
         if weight is not None:
             self._want(weight, "head norm weight", (torch.float32,), 1)
-            if weight.shape[0] != value_dim:
-                raise KernelError(f"head_norm_gate: weight {tuple(weight.shape)} for heads of {value_dim}")
+            if weight.shape[0] not in (value_dim, heads * value_dim):
+                raise KernelError(f"head_norm_gate: weight {tuple(weight.shape)} for {heads} heads of {value_dim}")
         act = {None: 0, "sigmoid": 1, "silu": 2}.get(activation, -1)
         if act < 0:
             raise KernelError(f"head_norm_gate: activation {activation!r} is not one of None, 'sigmoid', 'silu'")
@@ -916,7 +931,8 @@ class CudaOps(Ops):
             if gate.shape[0] != n or gate_offset + heads * value_dim > ldg or act == 0:
                 raise KernelError(f"head_norm_gate: gate {tuple(gate.shape)} from column {gate_offset}, activation {activation!r}")
         seq_row = self._step_rows(n)
-        self._check(self.seq.fz_head_norm_gate(_p(o), c_int(n), c_int(heads), c_int(value_dim), _p(weight), c_float(eps),
+        per_head = 1 if weight is not None and heads > 1 and weight.shape[0] == heads * value_dim else 0
+        self._check(self.seq.fz_head_norm_gate(_p(o), c_int(n), c_int(heads), c_int(value_dim), _p(weight), c_int(per_head), c_float(eps),
                                                _p(gate), c_int(ldg), c_int(gate_offset), c_int(act if gate is not None else 0),
                                                _p(seq_row), _p(out), c_int(_CODE[out.dtype]), self._stream()),
                     "head_norm_gate", n * heads * value_dim * (4 + (4 if gate is not None else 0) + out.element_size()))
@@ -947,24 +963,36 @@ class CudaOps(Ops):
             raise KernelError("key and value pools have different strides")
         return k, v
 
-    def rotate_kv_write(self, qkv, cos, sin, rotated, pairing, meta, cache, q_out, num_heads, num_kv_heads, key_dim, value_dim) -> None:
+    def rotate_kv_write(self, qkv, cos, sin, rotated, pairing, meta, cache, q_out, num_heads, num_kv_heads, key_dim, value_dim,
+                        q_norm=None, k_norm=None, norm_eps: float = 0.0, query_temperature=None) -> None:
         self._want(qkv, "qkv", (torch.float32,), 2)
         self._want(q_out, "q", (self.dtype,), 2)
         n = qkv.shape[0]
-        if qkv.shape[1] != (num_heads + num_kv_heads) * key_dim + num_kv_heads * value_dim or tuple(q_out.shape) != (n, num_heads * key_dim):
+        need = (num_heads + num_kv_heads) * key_dim + num_kv_heads * value_dim if cache.write else num_heads * key_dim
+        if qkv.shape[1] < need or tuple(q_out.shape) != (n, num_heads * key_dim):
             raise KernelError(f"rotate_kv_write: qkv {tuple(qkv.shape)}, q {tuple(q_out.shape)}")
+        for w, name in ((q_norm, "q norm weight"), (k_norm, "k norm weight")):
+            if w is not None:
+                self._want(w, name, (torch.float32,), 1)
+                if w.shape[0] != key_dim:
+                    raise KernelError(f"rotate_kv_write: {name} {tuple(w.shape)} for heads of {key_dim}")
+        if cache.write and (q_norm is None) != (k_norm is None):
+            raise KernelError("rotate_kv_write: queries and keys are normed together or not at all")
+        coef, every = (float(query_temperature[0]), int(query_temperature[1])) if query_temperature is not None else (0.0, 0)
+        self._meta_rows = meta.seq_row
         max_pos = self._tables(cos, sin, rotated, "rotate_kv_write")
         k, v = self._kv_views(cache, num_kv_heads, key_dim, value_dim)
         table = meta.table(cache.group)
         self._check(self.seq.fz_rotate_kv_write(
-            _p(qkv), _p(cos if rotated else None), _p(sin if rotated else None), c_int(rotated), c_int(pairing), c_int(max_pos),
+            _p(qkv), c_int(qkv.shape[1]), _p(cos if rotated else None), _p(sin if rotated else None), c_int(rotated), c_int(pairing), c_int(max_pos),
             _p(meta.pos), _p(meta.seq_row), _p(table), c_int(table.shape[1]), _p(k), _p(v), c_longlong(k.stride(0)),
             c_longlong(k.stride(1)), c_longlong(k.stride(2)), c_int(cache.page_size), c_int(k.shape[0]),
             c_int(1 if cache.write else 0), _p(q_out), c_int(_CODE[self.dtype]), c_int(n), c_int(num_heads), c_int(num_kv_heads),
-            c_int(key_dim), c_int(value_dim), _p(self.err), self._stream()), "rotate_kv_write",
-            n * qkv.shape[1] * (4 + q_out.element_size()))
+            c_int(key_dim), c_int(value_dim), _p(q_norm), _p(k_norm), c_float(norm_eps), c_float(coef), c_int(every),
+            _p(self.err), self._stream()), "rotate_kv_write", n * need * (4 + q_out.element_size()))
 
-    def sink_attention(self, q, cache, meta, out, num_heads, num_kv_heads, key_dim, value_dim, scale, window, keep_first, sink) -> None:
+    def sink_attention(self, q, cache, meta, out, num_heads, num_kv_heads, key_dim, value_dim, scale, window, keep_first, sink,
+                       softcap: float = 0.0, gate=None) -> None:
         self._want(q, "q", (self.dtype,), 2)
         self._want(out, "attention output", (self.dtype,), 2)
         n = q.shape[0]
@@ -974,6 +1002,13 @@ class CudaOps(Ops):
             self._want(sink, "sinks", (torch.float32,), 1)
             if sink.shape[0] != num_heads:
                 raise KernelError(f"sink_attention: {tuple(sink.shape)} sinks for {num_heads} heads")
+        g, g_off, g_ld = None, 0, 0
+        if gate is not None:
+            g, g_off = gate
+            self._want(g, "head gates", (torch.float32,), 2)
+            g_ld = g.shape[1]
+            if g.shape[0] != n or g_off < 0 or g_off + num_heads > g_ld:
+                raise KernelError(f"sink_attention: gates {tuple(g.shape)} from column {g_off} for {num_heads} heads")
         k, v = self._kv_views(cache, num_kv_heads, key_dim, value_dim)
         table = meta.table(cache.group)
         nbytes = 0
@@ -988,7 +1023,7 @@ class CudaOps(Ops):
         n_seg = getattr(meta, "max_segments", meta.n_segments)
         # prompt portions (bfloat16, keys and values of size 64 or 128): tiles of 64 rows on tensor cores
         if self.use_tensor_cores and self.sink_tensor_cores and self.dtype == torch.bfloat16 and max_portion >= SINK_MMA_ROWS and \
-                key_dim == value_dim and key_dim in (64, 128) and self.seq_tc.fz_sink_attention_mma_check(
+                not softcap and g is None and key_dim == value_dim and key_dim in (64, 128) and self.seq_tc.fz_sink_attention_mma_check(
                     c_int(num_heads), c_int(num_kv_heads), c_int(key_dim), c_int(value_dim), _p(k), _p(v), c_longlong(k.stride(0)),
                     c_longlong(k.stride(1)), c_longlong(k.stride(2))) == 0:
             self._check(self.seq_tc.fz_sink_attention_mma(
@@ -1011,9 +1046,73 @@ class CudaOps(Ops):
             c_longlong(k.stride(1)), c_longlong(k.stride(2)), c_int(cache.page_size), c_int(k.shape[0]), _p(out),
             c_int(_CODE[self.dtype]), c_int(n), c_int(num_heads), c_int(num_kv_heads), c_int(key_dim), c_int(value_dim),
             c_float(scale), c_int(window), c_int(keep_first), _p(sink), c_int(unit_chunks), c_int(units), _p(part),
-            _p(self.err), self._stream()), "sink_attention", nbytes)
+            c_float(softcap), _p(g), c_int(g_ld), c_int(g_off), _p(self.err), self._stream()), "sink_attention", nbytes)
         if units:
             self.launches += 1      # the merge kernel
+
+    def general_delta_scan(self, proj, heads, key_dim, value_dim, remove_offset, decay_in, decay_bias, remove_bias, decay_rate,
+                           unit_eps, state, meta, out) -> None:
+        self._want(proj, "delta-rule projections", (torch.float32,), 2)
+        self._want(decay_in, "decay inputs", (torch.float32,), 2)
+        self._want(decay_bias, "decay bias", (torch.float32,), 1)
+        self._want(remove_bias, "removal bias", (torch.float32,), 1)
+        self._want(out, "delta-rule output", (torch.float32,), 2)
+        n, ld = proj.shape
+        hk = heads * key_dim
+        if ld < 2 * hk + heads * value_dim or not 0 <= remove_offset <= ld - hk or tuple(decay_in.shape) != (n, hk) or \
+                decay_bias.shape[0] != hk or remove_bias.shape[0] != hk or tuple(out.shape) != (n, heads * value_dim):
+            raise KernelError(f"general_delta_scan: proj {tuple(proj.shape)}, decay inputs {tuple(decay_in.shape)}, "
+                              f"out {tuple(out.shape)}, removal inputs from column {remove_offset}")
+        self._state(state, heads, key_dim, value_dim, "general_delta_scan")
+        self._meta_rows = meta.seq_row
+        self._check(self.seq.fz_general_delta_scan(
+            _p(proj), c_int(ld), c_int(heads), c_int(key_dim), c_int(value_dim), c_int(remove_offset), _p(decay_in),
+            _p(decay_bias), _p(remove_bias), c_float(decay_rate), c_float(unit_eps), _p(state), _p(meta.seg),
+            c_int(meta.max_segments), _p(out), self._stream()), "general_delta_scan",
+            n * heads * (4 * key_dim + 2 * value_dim) * 4 + 2 * meta.n_segments * heads * value_dim * state.shape[3] * 4)
+
+    def activate(self, src, offset, kind, out) -> None:
+        self._want(src, "activation input", (torch.float32,), 2)
+        self._want(out, "activation output", (torch.float32, self.dtype), 2)
+        code = {"tanh": 0, "sigmoid": 1, "silu": 2, "gelu_tanh": 3}.get(kind)
+        n, w = out.shape
+        if code is None or src.shape[0] != n or offset < 0 or offset + w > src.shape[1]:
+            raise KernelError(f"activate: kind {kind!r}, src {tuple(src.shape)} from column {offset}, out {tuple(out.shape)}")
+        self._check(self.rows.fz_activate(_p(src), c_int(src.shape[1]), c_int(offset), c_int(code), _p(out),
+                                          c_int(_CODE[out.dtype]), c_int(n), c_int(w), self._stream()), "activate",
+                    n * w * (4 + out.element_size()))
+
+    def hashed_pair_embed(self, table, token_ids, meta, state, buckets, mul_prev, mul_cur, x) -> None:
+        self._want(table, "pair table", (torch.float32, torch.bfloat16), 2)
+        self._want(token_ids, "token ids", (torch.int32,), 1)
+        self._want(state, "previous tokens", (torch.int32,), 2)
+        self._want(x, "x", (torch.float32,), 2)
+        n, d = x.shape
+        if tuple(table.shape) != (buckets + 1, d) or token_ids.shape[0] != n or state.shape[1] != 1:
+            raise KernelError(f"hashed_pair_embed: table {tuple(table.shape)} for {buckets} buckets, ids {tuple(token_ids.shape)}, "
+                              f"x {tuple(x.shape)}, state {tuple(state.shape)}")
+        self._check(self.rows.fz_hashed_pair_embed(
+            _p(table), c_int(_CODE[table.dtype]), _p(token_ids), _p(meta.seq_row), _p(meta.seg), _p(state), c_int(buckets),
+            c_longlong(mul_prev), c_longlong(mul_cur), c_int(2 ** 31 - 1), _p(x), c_int(n), c_int(d), _p(self.err),
+            self._stream()), "hashed_pair_embed", n * d * (table.element_size() + 8))
+
+    def depth_average(self, streams, depth, coef, x, delta) -> None:
+        self._want(streams, "kept streams", (torch.float32,), 3)
+        self._want(x, "x", (torch.float32,), 2)
+        n, d = x.shape
+        if streams.shape[0] != n or streams.shape[2] != d or not -1 <= depth < streams.shape[1] - 1 or (coef is None) != (depth == -1):
+            raise KernelError(f"depth_average: streams {tuple(streams.shape)}, x {tuple(x.shape)}, depth {depth}")
+        if coef is not None:
+            self._want(coef, "depth weights", (torch.float32,), 1)
+            if coef.shape[0] != depth + 2:
+                raise KernelError(f"depth_average: {coef.shape[0]} weights at depth {depth}")
+        if delta is not None:
+            self._want(delta, "delta", (torch.float32,), 2)
+            if delta.shape != x.shape:
+                raise KernelError(f"depth_average: delta {tuple(delta.shape)} vs x {tuple(x.shape)}")
+        self._check(self.rows.fz_depth_average(_p(streams), c_int(streams.shape[1]), c_int(depth), _p(coef), _p(x), _p(delta),
+                                               c_int(n), c_int(d), self._stream()), "depth_average",
+                    n * d * 4 * (depth + 4 + (delta is not None)))
 
     def weighted_sum(self, terms, weights, out) -> None:
         if not 1 <= len(terms) <= 4 or len(weights) != len(terms):
