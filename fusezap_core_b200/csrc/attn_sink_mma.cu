@@ -24,7 +24,8 @@ sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
                           const int* __restrict__ seq_row, const int* __restrict__ table, int mb, long long page_stride,
                           long long head_stride, long long tok_stride, int page_size, int n_pages,
                           __nv_bfloat16* __restrict__ out, int Hq, int Hkv, float scale_log2, int window, int keep_first,
-                          const float* __restrict__ sink, int N, int* err) {
+                          const float* __restrict__ sink, float cap_log2, float over_cap, const float* __restrict__ gate,
+                          int gate_ld, int gate_off, int N, int* err) {
   fz_grid_launch_dependents();
   fz_grid_wait();
   constexpr int KSTEPS = HD / 16, NB = HD / 8, TILE_BYTES = BN * HD * 2;
@@ -131,7 +132,9 @@ sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
           const int key = key0 + 8 * j + 2 * (lane & 3) + (e & 1);
           const int qpos = qp[e >> 1];
           const bool ok = key <= qpos && (window <= 0 || key >= qpos - window + 1 || key < keep_first);
-          const float v = ok ? s[j][e] * scale_log2 : -INFINITY;
+          // (a cap c > 0: the scaled score x becomes c tanh(x / c); cap_log2 = c log2(e), over_cap = scale / c)
+          const float x = cap_log2 > 0.f ? cap_log2 * tanhf(s[j][e] * over_cap) : s[j][e] * scale_log2;
+          const float v = ok ? x : -INFINITY;
           s[j][e] = v;
           mx[e >> 1] = fmaxf(mx[e >> 1], v);
         }
@@ -192,7 +195,9 @@ sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
       corr = exp2f(m_run[hh] - mn);
       l = l * corr + exp2f(sk2 - mn);
     }
-    const float inv = corr / l;
+    float inv = corr / l;
+    if (gate != nullptr)                           // a gate per head: the result times its sigmoid
+      inv *= 1.0f / (1.0f + expf(-gate[(size_t)(row0 + r_off + r) * gate_ld + gate_off + h]));
     __nv_bfloat16* orow = out + (size_t)(row0 + r_off + r) * Hq * HD + (size_t)h * HD + 2 * (lane & 3);
 #pragma unroll
     for (int i = 0; i < NB; ++i)
@@ -203,8 +208,8 @@ sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
 template <int HD>
 int launch(const void* q, const void* k_pool, const void* v_pool, const int* seg, const int* seq_row, int n_seg, int max_portion,
            const int* table, int mb, long long page_stride, long long head_stride, long long tok_stride, int page_size,
-           int n_pages, void* out, int N, int Hq, int Hkv, float scale, int window, int keep_first, const float* sink, int* err,
-           cudaStream_t stream) {
+           int n_pages, void* out, int N, int Hq, int Hkv, float scale, int window, int keep_first, const float* sink,
+           float softcap, const float* gate, int gate_ld, int gate_off, int* err, cudaStream_t stream) {
   constexpr size_t smem = 4 * (BN * HD * 2) + BM * HD * 2;
   static bool raised = false;
   if (smem > 48 * 1024 && !raised) {
@@ -216,7 +221,8 @@ int launch(const void* q, const void* k_pool, const void* v_pool, const int* seg
   if (tiles > 65535 || Hq > 65535) return FZ_TOO_LARGE;
   fz_launch(sink_attention_mma_kernel<HD>, dim3(n_seg + 1, tiles, Hq), dim3(THREADS), smem, stream, (const __nv_bfloat16*)q,
             (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, seg, seq_row, table, mb, page_stride, head_stride,
-            tok_stride, page_size, n_pages, (__nv_bfloat16*)out, Hq, Hkv, scale * LOG2E, window, keep_first, sink, N, err);
+            tok_stride, page_size, n_pages, (__nv_bfloat16*)out, Hq, Hkv, scale * LOG2E, window, keep_first, sink,
+            softcap > 0.f ? softcap * LOG2E : 0.f, softcap > 0.f ? scale / softcap : 0.f, gate, gate_ld, gate_off, N, err);
   FZ_LAUNCH_CHECK();
   return FZ_OK;
 }
@@ -233,16 +239,17 @@ FZ_API int fz_sink_attention_mma_check(int Hq, int Hkv, int dk, int dv, const vo
 FZ_API int fz_sink_attention_mma(const void* q, const void* k_pool, const void* v_pool, const int* seg, const int* seq_row,
                                  int n_seg, int max_portion, const int* table, int mb, long long page_stride,
                                  long long head_stride, long long tok_stride, int page_size, int n_pages, void* out, int N,
-                                 int Hq, int Hkv, int hd, float scale, int window, int keep_first, const float* sink, int* err,
-                                 cudaStream_t stream) {
+                                 int Hq, int Hkv, int hd, float scale, int window, int keep_first, const float* sink,
+                                 float softcap, const float* gate, int gate_ld, int gate_off, int* err, cudaStream_t stream) {
   if (N <= 0 || n_seg <= 0) return FZ_OK;
+  if (softcap < 0.f || (gate != nullptr && (gate_off < 0 || gate_off + Hq > gate_ld))) return FZ_BAD_SHAPE;
   if (fz_sink_attention_mma_check(Hq, Hkv, hd, hd, k_pool, v_pool, page_stride, head_stride, tok_stride) != FZ_OK ||
       page_size <= 0 || max_portion <= 0 || window < 0 || keep_first < 0 || ((uintptr_t)q & 15)) return FZ_BAD_SHAPE;
   if (hd == 64)
     return launch<64>(q, k_pool, v_pool, seg, seq_row, n_seg, max_portion, table, mb, page_stride, head_stride, tok_stride,
-                      page_size, n_pages, out, N, Hq, Hkv, scale, window, keep_first, sink, err, stream);
+                      page_size, n_pages, out, N, Hq, Hkv, scale, window, keep_first, sink, softcap, gate, gate_ld, gate_off, err, stream);
   return launch<128>(q, k_pool, v_pool, seg, seq_row, n_seg, max_portion, table, mb, page_stride, head_stride, tok_stride,
-                     page_size, n_pages, out, N, Hq, Hkv, scale, window, keep_first, sink, err, stream);
+                     page_size, n_pages, out, N, Hq, Hkv, scale, window, keep_first, sink, softcap, gate, gate_ld, gate_off, err, stream);
 }
 
 #ifdef FZ_TIMELINE

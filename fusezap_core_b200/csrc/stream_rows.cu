@@ -62,6 +62,51 @@ depth_average_kernel(float* __restrict__ streams, int L1, int depth, const float
   }
 }
 
+// `depth_average_kernel` and the RMS norm of its result in one pass over the row: h = w * x * rsqrt(mean(x^2) + eps) of
+// the averaged x. rows == nullptr: one block per row n, the kept stream and x are written as the unfused kernel writes
+// them. rows != nullptr: block r reads row rows[r] and writes only h[r] (rows[r] < 0 gives zeros). The averaged row
+// waits in shared memory (D floats) between the two passes.
+template <typename TH>
+__global__ void __launch_bounds__(256)
+depth_average_norm_kernel(float* __restrict__ streams, int L1, int depth, const float* __restrict__ coef, float* __restrict__ x,
+                          const float* __restrict__ delta, int D, const float* __restrict__ w, float eps, TH* __restrict__ h,
+                          const int* __restrict__ rows, int n_src, int* err) {
+  fz_grid_launch_dependents();
+  fz_grid_wait();
+  extern __shared__ __align__(16) float avg[];
+  __shared__ float scratch[32];
+  const int r = blockIdx.x;
+  int n = r;
+  TH* hr = h + (size_t)r * D;
+  if (rows != nullptr) {
+    n = rows[r];
+    if (n < 0 || n >= n_src) {
+      if (n >= n_src && threadIdx.x == 0) atomicOr(err, FZ_ERR_ROW_RANGE);
+      for (int d = threadIdx.x; d < D; d += blockDim.x) hr[d] = Cvt<TH>::from_f(0.f);
+      return;
+    }
+  }
+  float* st = streams + (size_t)n * L1 * D;
+  float* xr = x + (size_t)n * D;
+  const float* dr = delta != nullptr ? delta + (size_t)n * D : nullptr;
+  float ss = 0.f;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    const float X = dr != nullptr ? xr[d] + dr[d] : xr[d];
+    float acc = 0.f;
+    for (int j = 0; j <= depth; ++j) acc = fmaf(coef[j], st[(size_t)j * D + d], acc);
+    acc = fmaf(coef[depth + 1], X, acc);
+    if (rows == nullptr) {
+      st[(size_t)(depth + 1) * D + d] = X;
+      xr[d] = acc;
+    }
+    avg[d] = acc;
+    ss = fmaf(acc, acc, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float scale = 1.0f / sqrtf(ss * (1.0f / (float)D) + eps);
+  for (int d = threadIdx.x; d < D; d += blockDim.x) hr[d] = Cvt<TH>::from_f(w[d] * (avg[d] * scale));
+}
+
 // out[n, j] = act(src[n, off + j]). kind 0: tanh, 1: sigmoid, 2: silu, 3: the tanh form of gelu.
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -103,6 +148,37 @@ FZ_API int fz_depth_average(float* streams, int L1, int depth, const float* coef
   if (N <= 0 || D <= 0) return FZ_OK;
   if (depth < -1 || depth + 1 >= L1 || (coef == nullptr) != (depth == -1)) return FZ_BAD_SHAPE;
   fz_launch(depth_average_kernel, dim3(N), dim3(256), 0, stream, streams, L1, depth, coef, x, delta, D);
+  FZ_LAUNCH_CHECK();
+  return FZ_OK;
+}
+
+// n_out blocks: the rows of the step (rows null, n_out = n_src) or the selected ones. w: D float32 values.
+FZ_API int fz_depth_average_norm(float* streams, int L1, int depth, const float* coef, float* x, const float* delta, int n_src,
+                                 int D, const float* w, float eps, void* h, int h_dtype, const int* rows, int n_out, int* err,
+                                 cudaStream_t stream) {
+  if (n_out <= 0 || D <= 0) return FZ_OK;
+  if (depth < 0 || depth + 1 >= L1 || coef == nullptr || w == nullptr) return FZ_BAD_SHAPE;
+  const size_t smem = sizeof(float) * (size_t)D;
+  if (smem > 200 * 1024) return FZ_TOO_LARGE;
+  if (h_dtype == FZ_F32) {
+    static size_t allowed = 48 * 1024;
+    if (smem > allowed) {
+      cudaError_t e = cudaFuncSetAttribute(depth_average_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+      allowed = smem;
+    }
+    fz_launch(depth_average_norm_kernel<float>, dim3(n_out), dim3(256), smem, stream, streams, L1, depth, coef, x, delta, D, w,
+              eps, (float*)h, rows, n_src, err);
+  } else if (h_dtype == FZ_BF16) {
+    static size_t allowed = 48 * 1024;
+    if (smem > allowed) {
+      cudaError_t e = cudaFuncSetAttribute(depth_average_norm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+      allowed = smem;
+    }
+    fz_launch(depth_average_norm_kernel<__nv_bfloat16>, dim3(n_out), dim3(256), smem, stream, streams, L1, depth, coef, x, delta,
+              D, w, eps, (__nv_bfloat16*)h, rows, n_src, err);
+  } else return FZ_BAD_DTYPE;
   FZ_LAUNCH_CHECK();
   return FZ_OK;
 }

@@ -169,7 +169,7 @@ class Ops:
         by token, per head: u = k / sqrt(sum k^2 + unit_eps), d = exp(-decay_rate * sigmoid(decay_in + decay_bias)),
         a = sigmoid(remove + remove_bias) per key channel; with b = S^T u of the state before the token,
         S = diag(d) S - (a * u) b^T + k v^T, out[n, h] = S^T r. float32 throughout; out (N, H dv); the state
-        (`recurrent_state_shape`) is that after the portion's last token. Padding rows give zeros."""
+        (`recurrent_state_shape`) is that after the portion's last token. Rows of padding are left as they are."""
         raise NotImplementedError
 
     def activate(self, src: torch.Tensor, offset: int, kind: str, out: torch.Tensor) -> None:
@@ -189,8 +189,17 @@ class Ops:
                       delta: torch.Tensor | None) -> None:
         """streams: (N, L + 1, D) float32; x, delta (N, D) float32 (delta None: zero). streams[:, depth + 1] = x + delta;
         then x = sum_j coef[j] * streams[:, j] over j = 0 .. depth + 1 in rising j (coef float32, depth + 2 numbers),
-        each product rounded, in float32. depth -1 with coef None: streams[:, 0] = x + delta and x = x + delta."""
+        by fused multiply-adds from zero, in float32. depth -1 with coef None: streams[:, 0] = x + delta and x = x + delta."""
         raise NotImplementedError
+
+    def depth_average_rmsnorm(self, streams: torch.Tensor, depth: int, coef: torch.Tensor, x: torch.Tensor,
+                              delta: torch.Tensor | None, weight: torch.Tensor, eps: float, h: torch.Tensor,
+                              rows: torch.Tensor | None = None) -> bool:
+        """`depth_average` followed by `add_rmsnorm(x, None, weight, eps, h, rows)` as one operation. rows None: streams and
+        x are written as `depth_average` writes them and h[n] is the norm of the averaged row. rows (int32 (R,), -1 =
+        none): only h[r], from row rows[r], is written. Optional: returns False, having done nothing, if this table has
+        no such kernel for these sizes; the caller then runs the two operations."""
+        return False
 
     def check_sink_attention(self, num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int) -> None:
         """Raise ValueError if `sink_attention` cannot take these sizes."""

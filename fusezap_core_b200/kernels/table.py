@@ -125,6 +125,7 @@ class CudaOps(Ops):
         self.prefill_tcgen05 = True        # False: long portions on the mma.sync flash-attention kernel
         self.fuse_swiglu = True            # gate/up product and SwiGLU in one kernel where the sizes allow it
         self.fuse_argmax = True            # lm_head product and argmax in one pass where no logits are asked for
+        self.fuse_depth_norm = True        # the depth average of a layer's result and the norm that follows in one kernel
         self.fuse_rope = True              # q/k/v product, rotation and cache write in one kernel (few-token steps)
         # 128-row tiles for experts with hundreds of rows: measured slower for the gated product (347 against 319 us at
         # 8,192 pairs x 2,048 x 1,024) and the same for the scatter product (199 against 205 us), so off
@@ -1023,15 +1024,15 @@ class CudaOps(Ops):
         n_seg = getattr(meta, "max_segments", meta.n_segments)
         # prompt portions (bfloat16, keys and values of size 64 or 128): tiles of 64 rows on tensor cores
         if self.use_tensor_cores and self.sink_tensor_cores and self.dtype == torch.bfloat16 and max_portion >= SINK_MMA_ROWS and \
-                not softcap and g is None and key_dim == value_dim and key_dim in (64, 128) and self.seq_tc.fz_sink_attention_mma_check(
+                key_dim == value_dim and key_dim in (64, 128) and self.seq_tc.fz_sink_attention_mma_check(
                     c_int(num_heads), c_int(num_kv_heads), c_int(key_dim), c_int(value_dim), _p(k), _p(v), c_longlong(k.stride(0)),
                     c_longlong(k.stride(1)), c_longlong(k.stride(2))) == 0:
             self._check(self.seq_tc.fz_sink_attention_mma(
                 _p(q), _p(k), _p(v), _p(meta.seg), _p(meta.seq_row), c_int(n_seg), c_int(max_portion), _p(table),
                 c_int(table.shape[1]), c_longlong(k.stride(0)), c_longlong(k.stride(1)), c_longlong(k.stride(2)),
                 c_int(cache.page_size), c_int(k.shape[0]), _p(out), c_int(n), c_int(num_heads), c_int(num_kv_heads),
-                c_int(key_dim), c_float(scale), c_int(window), c_int(keep_first), _p(sink), _p(self.err), self._stream()),
-                "sink_attention (tensor cores)", nbytes)
+                c_int(key_dim), c_float(scale), c_int(window), c_int(keep_first), _p(sink), c_float(softcap), _p(g), c_int(g_ld),
+                c_int(g_off), _p(self.err), self._stream()), "sink_attention (tensor cores)", nbytes)
             return
         unit_chunks = units = 0
         part = None
@@ -1113,6 +1114,30 @@ class CudaOps(Ops):
         self._check(self.rows.fz_depth_average(_p(streams), c_int(streams.shape[1]), c_int(depth), _p(coef), _p(x), _p(delta),
                                                c_int(n), c_int(d), self._stream()), "depth_average",
                     n * d * 4 * (depth + 4 + (delta is not None)))
+
+    def depth_average_rmsnorm(self, streams, depth, coef, x, delta, weight, eps, h, rows=None) -> bool:
+        if not self.fuse_depth_norm or depth < 0 or weight.dtype != torch.float32:
+            return False
+        self._want(streams, "kept streams", (torch.float32,), 3)
+        self._want(x, "x", (torch.float32,), 2)
+        self._want(coef, "depth weights", (torch.float32,), 1)
+        self._want(weight, "norm weight", (torch.float32,), 1)
+        self._want(h, "h", (torch.float32, torch.bfloat16), 2)
+        n, d = x.shape
+        n_out = n
+        if rows is not None:
+            self._want(rows, "rows", (torch.int32,), 1)
+            n_out = rows.shape[0]
+        if streams.shape[0] != n or streams.shape[2] != d or depth >= streams.shape[1] - 1 or coef.shape[0] != depth + 2 or \
+                tuple(h.shape) != (n_out, d) or weight.shape[0] != d or (delta is not None and delta.shape != x.shape):
+            raise KernelError(f"depth_average_rmsnorm: streams {tuple(streams.shape)}, x {tuple(x.shape)}, h {tuple(h.shape)}, depth {depth}")
+        if delta is not None:
+            self._want(delta, "delta", (torch.float32,), 2)
+        self._check(self.rows.fz_depth_average_norm(
+            _p(streams), c_int(streams.shape[1]), c_int(depth), _p(coef), _p(x), _p(delta), c_int(n), c_int(d), _p(weight),
+            c_float(eps), _p(h), c_int(_CODE[h.dtype]), _p(rows), c_int(n_out), _p(self.err), self._stream()),
+            "depth_average + rmsnorm", n_out * d * (4 * (depth + 3 + (delta is not None)) + h.element_size()))
+        return True
 
     def weighted_sum(self, terms, weights, out) -> None:
         if not 1 <= len(terms) <= 4 or len(weights) != len(terms):

@@ -7,14 +7,34 @@ stream that layer i + 1 (or the model's last norm) reads is
 
 c_i being layer i's tensor `name` of i + 2 numbers. The block wraps any other block (`inner`), which computes X_(i+1)
 from x as it would without the averaging. The X_j of a step live in one scratch buffer (rows, depths + 1, width) that the
-layers of the model share; sums and products are 32-bit, the terms added in rising j.
+layers of the model share; sums and products are 32-bit, the terms added in rising j. The sum is handed on unevaluated
+(`PendingDepthAverage`) so that the next norm takes it in its own pass over the row, as it takes a pending residual term.
 """
 from __future__ import annotations
 import torch
 
+from dataclasses import dataclass
+
 from ..config import PartSpec
 from ..weights import ParamSpec
 from .base import BLOCKS, Block, LayerCache, register_block
+
+
+@dataclass
+class PendingDepthAverage:
+    """What a depth-averaged layer hands on in place of a pending residual term: the sum has not been taken yet, so that
+    the norm that reads the stream next can take it in the same pass (`Norm` parts look for `fold_into_norm`). A
+    consumer that cannot fold it calls `resolve`, which runs the plain operation."""
+    streams: torch.Tensor
+    depth: int
+    coef: torch.Tensor
+    delta: torch.Tensor | None
+
+    def fold_into_norm(self, ctx, x, weight, eps, h, rows) -> bool:
+        return bool(ctx.ops.depth_average_rmsnorm(self.streams, self.depth, self.coef, x, self.delta, weight, eps, h, rows))
+
+    def resolve(self, ctx, x) -> None:
+        ctx.ops.depth_average(self.streams, self.depth, self.coef, x, self.delta)
 
 
 @register_block("depth_average")
@@ -49,8 +69,9 @@ class DepthAverageBlock(Block):
         ops = ctx.ops
         hist = ctx.ws.get("depth_streams", (x.shape[0], self.depths + 1, self.D), torch.float32)
         if self.depth == 0:
+            if hasattr(delta, "resolve"):
+                delta = delta.resolve(ctx, x)
             ops.depth_average(hist, -1, None, x, delta)      # X_0: the stream as the embedding left it
             delta = None
         x, delta = self.inner.forward(ctx, x, delta, cache)
-        ops.depth_average(hist, self.depth, self.coef, x, delta)
-        return x, None
+        return x, PendingDepthAverage(hist, self.depth, self.coef, delta)

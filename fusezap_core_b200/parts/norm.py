@@ -43,6 +43,12 @@ class RMSNorm(Norm):
         self._run(ctx, x, None, h, None)
 
     def _run(self, ctx, x, delta, h, rows) -> None:
+        if hasattr(delta, "fold_into_norm"):       # a pending operation on the stream that this norm can take in its pass
+            if self.groups == 1 and delta.fold_into_norm(ctx, x, self.weight, self.eps, h, rows):
+                return
+            if rows is not None:
+                raise NotImplementedError("a pending operation on the stream cannot be resolved for selected rows only")
+            delta = delta.resolve(ctx, x)
         if self.groups == 1:
             ctx.ops.add_rmsnorm(x, delta, self.weight, self.eps, h, rows)
         else:

@@ -63,6 +63,41 @@ CONFIGS = {"mix": (NEP_MIX, 3), "odd": (NEP_ODD, 5), "one": (NEP_ONE, 9)}
 STD_SCALE = 5.0
 
 
+def drawn_config(seed: int) -> dict:
+    """A configuration drawn from a seed: odd and even sizes, the three layer types in any order, grouped and ungrouped
+    heads, key and value sizes equal and unequal (the sizes 64 and 128 among them), heads rotated in part and in whole
+    with and without scaled frequencies, windows from a few tokens to longer than the sequence, temperature periods of
+    one token and more, caps below and above the scores, caches read by later layers, layers without feed-forward."""
+    rng = np.random.default_rng(1000 + seed)
+    pick = lambda *xs: xs[int(rng.integers(len(xs)))]
+    layers, owners = [], []
+    for i in range(int(rng.integers(2, 7))):
+        ff = int(pick(0, 16, 36, 64))
+        kind = pick("attention", "attention", "attention_2", "general_delta")
+        if kind == "general_delta":
+            layers.append(_layer(kind, {"heads": int(pick(1, 2, 3)), "dim": int(pick(8, 12, 20, 48, 64))}, ff))
+        elif kind == "attention_2":
+            kv, dk = int(pick(1, 2, 3)), int(pick(8, 12, 16, 40, 64, 128))
+            dims = int(pick(2, dk, dk // 2 // 2 * 2 or 2))
+            scaling = pick(None, (4.0, 16, 4.0, 0.5), (8.0, 64, 32.0, 1.0), (2.0, 2048, 32.0, 1.0))
+            layers.append(_layer(kind, _att2(kv * int(pick(1, 2, 3)), kv, dk, dk if dk >= 64 else int(pick(4, 8, 12, 40)), float(pick(0.2, 0.35)),
+                                             int(pick(1, 3, 7, 16, 64, 200)), float(pick(50.0, 10000.0, 250000.0)), dims, scaling), ff))
+        elif owners and rng.random() < 0.4:
+            j = int(pick(*owners))
+            m = dict(layers[j]["mixer"], scale=float(pick(0.15, 0.3)), softcap=float(pick(0.75, 5.0, 30.0)),
+                     q_temp={"coef": float(pick(0.1, 0.5, 1.5)), "every": int(pick(1, 2, 5, 256))}, kv_from=j)
+            layers.append(_layer(kind, m, ff))
+        else:
+            kv, dk = int(pick(1, 2, 3)), int(pick(8, 16, 24, 64, 96, 128))
+            owners.append(i)
+            layers.append(_layer(kind, _att(kv * int(pick(1, 2, 4)), kv, dk, dk if dk >= 64 else int(pick(8, 24, 40)), float(pick(0.1, 0.25)),
+                                            float(pick(0.1, 0.5, 1.5)), int(pick(1, 3, 16, 256)), float(pick(0.75, 5.0, 30.0))), ff))
+    return {"architecture": "Nepudra", "vocab": int(pick(37, 64, 150)), "width": int(pick(24, 40, 56, 72, 100)),
+            "norm": {"eps": float(pick(1e-6, 1e-5))},
+            "embedding": {"bigram": {"buckets": int(pick(1, 31, 1021)), "mul_prev": int(pick(0, 1, 31)), "mul_cur": int(pick(1, 17))}},
+            "layers": layers}
+
+
 def make_dir(name: str, tmp, cfg: dict | None = None, seed: int | None = None, change=None) -> tuple[str, dict, dict]:
     """Writes configuration `name` with seeded random weights (float32); `change(tensors)` may edit them before they
     are written. Returns (folder, config, weights by name)."""

@@ -116,8 +116,7 @@ def attention(cfg: dict, w: dict, p: str, m: dict, h: torch.Tensor, kv: tuple) -
         cos, sin = yarn_angles(m["rot"], n)
         q = rotate_halves(q, cos, sin, m["rot"]["dims"])
     if "q_temp" in m:
-        pos = torch.arange(n, dtype=F)
-        q = q * (1.0 + m["q_temp"]["coef"] * torch.log(torch.floor((pos + 1) / m["q_temp"]["every"]) + 1.0))[:, None, None]
+        q = q * query_temperature(m["q_temp"], torch.arange(n, dtype=F))[:, None, None]
     k, v = kv
     o = softmax_attention(q, k, v, m["scale"], m.get("mask", {}).get("size", 0), m.get("softcap", 0.0))
     o = o * sigmoid(h @ w[p + "g"].T)[:, :, None]
@@ -127,24 +126,48 @@ def attention(cfg: dict, w: dict, p: str, m: dict, h: torch.Tensor, kv: tuple) -
     return y
 
 
+def delta_recurrence(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, d: torch.Tensor, a: torch.Tensor,
+                     S: torch.Tensor | None = None, unit_eps: float = 1e-6) -> tuple[torch.Tensor, torch.Tensor]:
+    """r, k, d, a: (n, H, dk); v: (n, H, dv); S: (H, dk, dv) or None for zeros. Per token and head, with the unit key u:
+    S <- diag(d) S - (a u)(u^T S) + k v^T, both products from the state before the token; o = S^T r. Returns (o, S)."""
+    n, H, dk = k.shape
+    u = k / torch.sqrt((k * k).sum(-1, keepdim=True) + unit_eps)
+    S = torch.zeros(H, dk, v.shape[2], dtype=F) if S is None else S
+    o = torch.zeros(n, H, v.shape[2], dtype=F)
+    for t in range(n):
+        back = torch.einsum("hi,hij->hj", u[t], S)
+        S = d[t][:, :, None] * S - (a[t] * u[t])[:, :, None] * back[:, None, :] + k[t][:, :, None] * v[t][:, None, :]
+        o[t] = torch.einsum("hij,hi->hj", S, r[t])
+    return o, S
+
+
+def decay_of(z: torch.Tensor) -> torch.Tensor:
+    """The decay of a key channel from its input: exp(-exp(-1/2) * sigmoid(z))."""
+    return torch.exp(-math.exp(-0.5) * sigmoid(z))
+
+
 def general_delta(cfg: dict, w: dict, p: str, m: dict, h: torch.Tensor, state: torch.Tensor | None = None) -> torch.Tensor:
-    """S <- diag(d) S - (a u)(u^T S) + k v^T per head, both products from the state before the token; o = S^T r."""
+    """The generalized delta rule mixer: projections, decays and removal rates, the recurrence, head norm, gate, output."""
     n = h.shape[0]
     H, dim = m["heads"], m["dim"]
     r = (h @ w[p + "r"].T).view(n, H, dim)
     k = (h @ w[p + "k"].T).view(n, H, dim)
     v = (h @ w[p + "v"].T).view(n, H, dim)
-    d = torch.exp(-math.exp(-0.5) * sigmoid(torch.tanh(h @ w[p + "w1"].T) @ w[p + "w2"].T + w[p + "w0"])).view(n, H, dim)
+    d = decay_of(torch.tanh(h @ w[p + "w1"].T) @ w[p + "w2"].T + w[p + "w0"]).view(n, H, dim)
     a = sigmoid(h @ w[p + "a"].T + w[p + "a.b"]).view(n, H, dim)
-    u = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
-    S = torch.zeros(H, dim, dim, dtype=F) if state is None else state
-    o = torch.zeros(n, H, dim, dtype=F)
-    for t in range(n):
-        back = torch.einsum("hi,hij->hj", u[t], S)
-        S = d[t][:, :, None] * S - (a[t] * u[t])[:, :, None] * back[:, None, :] + k[t][:, :, None] * v[t][:, None, :]
-        o[t] = torch.einsum("hij,hi->hj", S, r[t])
+    o, _ = delta_recurrence(r, k, v, d, a, state)
     o = rms(o, cfg["norm"]["eps"]).reshape(n, -1) * w[p + "norm"] * sigmoid(h @ w[p + "g"].T)
     return o @ w[p + "o"].T
+
+
+def depth_average(streams: list, c: torch.Tensor) -> torch.Tensor:
+    """sum_j c[j] * streams[j] over all streams so far (the embedding output first)."""
+    return sum(c[j] * streams[j] for j in range(len(streams)))
+
+
+def query_temperature(q_temp: dict, positions: torch.Tensor) -> torch.Tensor:
+    """The factor of the queries at each position: 1 + coef * ln(floor((p + 1) / every) + 1)."""
+    return 1.0 + q_temp["coef"] * torch.log(torch.floor((positions + 1) / q_temp["every"]) + 1.0)
 
 
 def forward(cfg: dict, w: dict, tokens: list[int], layers: bool = False):
@@ -169,7 +192,7 @@ def forward(cfg: dict, w: dict, tokens: list[int], layers: bool = False):
         if L.get("mlp") is not None:
             x = x + feed_forward(w, p + "mlp.", scalar_norm(x, w[p + "norm2"], eps))
         streams.append(x)
-        x = sum(w[p + "dwa"][j] * streams[j] for j in range(i + 2))
+        x = depth_average(streams, w[p + "dwa"])
         after.append(x)
     logits = scalar_norm(x, w["final.norm"], eps) @ w["head"].T
     return (logits, torch.stack(after)) if layers else logits

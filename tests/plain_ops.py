@@ -537,3 +537,18 @@ class PlainOpsDeep(PlainOpsSeq):
                 g, off = gate
                 o = o * torch.sigmoid(g[i, off: off + Hq].float())[:, None]
             out[i] = o.reshape(-1).to(out.dtype)
+
+    def depth_average_rmsnorm(self, streams, depth, coef, x, delta, weight, eps, h, rows=None) -> bool:
+        if not getattr(self, "fuse_depth_norm", True):
+            return False
+        if rows is None:
+            self.depth_average(streams, depth, coef, x, delta)
+            self.add_rmsnorm(x, None, weight, eps, h)
+            return True
+        full = x + delta if delta is not None else x.clone()
+        acc = torch.zeros_like(full)
+        for j in range(depth + 1):
+            acc = acc + coef[j] * streams[:, j]
+        acc = acc + coef[depth + 1] * full
+        self.add_rmsnorm(acc, None, weight, eps, h, rows)
+        return True

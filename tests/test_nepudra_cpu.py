@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 import torch
 
-from nepudra_util import CONFIGS, NEP_MIX, NEP_ODD, make_dir, plain_logits, tokens_for
+from nepudra_util import CONFIGS, NEP_MIX, NEP_ODD, drawn_config, make_dir, plain_logits, tokens_for
 from pepilix_util import rel_rms, run_cut, run_mixed
 from plain_ops import PlainOpsDeep
 from fusezap_core_b200 import LLMEngine, SamplingParams
@@ -158,3 +158,16 @@ def test_greedy_generation_through_the_entry_point(dirs):
         for i, t in enumerate(new):
             row = lg[len(prompt) - 1 + i]
             assert int(row.argmax()) == t or row.max() - row[t] < 1e-3
+
+
+@pytest.mark.parametrize("seed", range(10))
+def test_configurations_drawn_at_random(seed, tmp_path):
+    """The host side reads every size and constant from the configuration: drawn ones (the GPU tests' own) against the
+    plain model, whole, in portions and token by token."""
+    cfg = drawn_config(seed)
+    d, cfg, w = make_dir(f"drawn{seed}", tmp_path, cfg, seed)
+    model, cache, runner = engine_parts(d, page=4, pages=30, slots=2, max_len=64)
+    toks = tokens_for(cfg, (40,), seed=seed)[0]
+    ref = plain_logits(cfg, w, toks)
+    for cuts in ((40,), (1,), (6, 2, 1, 17)):
+        assert rel_rms(run_cut(runner, cache, "r", toks, cuts), ref) < 2e-5, (seed, cuts)
