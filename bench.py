@@ -1,7 +1,7 @@
 """Benchmark: decode tokens per second of the Llama-3.1-8B-sized model (random bf16 weights) on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 4096] [--layers L] [--impl ours|reference]
-                    [--preset NAME] [--workload decode|stream|pepilix|gizulorn]
+                    [--preset NAME] [--workload decode|stream|pepilix|gizulorn|nepudra]
 
 A "step" is one decode step of `--batch` requests whose contexts end at `--context` tokens. Prints ONE JSON line:
   value      decoded tokens per second, timed on the device (CUDA events around K steps: metadata copy + graph replay)
@@ -25,6 +25,10 @@ arrival to the last token.
 
 `--workload gizulorn` (`--sizes g1024,g2048`, `--layers 4`) does the same for the Gizulorn design (retention, attention with
 a window and a sink beside the gated delta rule, routed experts with a shared one).
+`--workload nepudra` (`--sizes n1024,n2048`, `--layers 4`) does the same for the Nepudra design (attention with capped
+scores, a query temperature and head gates, layers that read an earlier layer's cache, windowed attention with normed and
+rotated heads, the generalized delta rule, depth-averaged layers, a hashed pair embedding) beside Gizulorn at equal width,
+layers, heads, window and dense feed-forward size.
 `--workload pepilix` (`--sizes w1024,w2048`, `--layers 4`) times the Pepilix design beside the dense decoder at equal
 width, layers, heads, vocabulary and active feed-forward size: a 2,048-token prompt and decode steps at `--batch`
 requests through `LLMEngine.step()`, and (unless `--no-points`) a kernel-by-kernel profile of both; its line's `sizes`
@@ -156,7 +160,7 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--reference-device", default="CUDA", help="the reference's device name for --impl reference")
-    ap.add_argument("--workload", default="decode", choices=["decode", "stream", "pepilix", "gizulorn"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "stream", "pepilix", "gizulorn", "nepudra"],
                     help="pepilix: prefill and decode of the Pepilix design at a few layer sizes, beside the dense decoder "
                          "at equal width, layers, heads and active feed-forward size")
     ap.add_argument("--sizes", default="w1024,w2048", help="pepilix workload: which of its sizes to run")
@@ -188,6 +192,8 @@ def main() -> int:
         return pepilix_workload(a)
     if a.workload == "gizulorn":
         return design_workload(a, "gizulorn")
+    if a.workload == "nepudra":
+        return design_workload(a, "nepudra")
 
     import numpy as np
     import torch
@@ -439,6 +445,48 @@ def gizulorn_configs(name: str, L: int, ctx: int):
     return giz, dense
 
 
+# Layer sizes for the Nepudra workload: (width, heads, kv heads, head size, window of the windowed layers, heads and head
+# size of the delta rule, ff, vocab). Layers cycle through attention (capped scores, query temperature), attention that
+# reads the cache of the layer before it, windowed attention (normed heads, scaled rotation) and the generalized delta
+# rule without feed-forward. Gizulorn beside it has the same width, layers, heads, head sizes, window, vocabulary and a
+# dense feed-forward of the same size; its layers alternate parallel (windowed attention with a sink beside the gated delta
+# rule) and retention, so each of Nepudra's kernels has a like kernel there.
+NEPUDRA_SIZES = {
+    "n1024": (1024, 8, 2, 128, 512, 16, 64, 4096, 32768),
+    "n2048": (2048, 16, 4, 128, 1024, 16, 128, 8192, 32768),
+}
+
+
+def nepudra_configs(name: str, L: int, ctx: int):
+    D, H, kv, hd, window, dh, dd, ff, V = NEPUDRA_SIZES[name]
+    mlp = {"kind": "dense", "ff": ff}
+    att = {"heads": H, "kv_heads": kv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "softcap": 30.0, "q_temp": {"coef": 0.1, "every": 1024}}
+    win = {"heads": H, "kv_heads": kv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "mask": {"size": window},
+           "rot": {"base": 5e5, "dims": hd, "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}}
+    layers = []
+    for i in range(L):
+        k = i % 4
+        if k == 0 or (k == 1 and i == 0):
+            layers.append({"type": "attention", "mixer": dict(att), "mlp": mlp})
+        elif k == 1:
+            layers.append({"type": "attention", "mixer": dict(att, kv_from=i - 1), "mlp": mlp})
+        elif k == 2:
+            layers.append({"type": "attention_2", "mixer": win, "mlp": mlp})
+        else:
+            layers.append({"type": "general_delta", "mixer": {"heads": dh, "dim": dd}, "mlp": None})
+    nep = {"architecture": "Nepudra", "vocab": V, "width": D, "norm": {"eps": 1e-6},
+           "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}}, "layers": layers}
+    ret = {"heads": dh, "dim": dd, "vdim": dd, "decay": [1.0 - 2.0 ** (-5 - 5 * h / max(1, dh - 1)) for h in range(dh)],
+           "rot": {"base": 1e6, "dims": dd}}
+    par = {"left": {"heads": H, "kv_heads": kv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "mask": {"size": window, "keep_first": 4},
+                    "rot": {"base": 5e5, "dims": hd, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}},
+           "left_scale": 0.8, "right": {"heads": dh, "kv_heads": dh, "dim": dd, "vdim": dd, "conv": 4}, "right_scale": 0.5}
+    giz = {"architecture": "Gizulorn", "vocab": V, "width": D, "norm": {"eps": 1e-6},
+           "layers": [{"type": "parallel" if i % 2 == 0 else "retention", "mixer": par if i % 2 == 0 else ret, "mlp": mlp}
+                      for i in range(L)]}
+    return nep, giz
+
+
 def pepilix_workload(a) -> int:
     return design_workload(a, "pepilix")
 
@@ -459,11 +507,14 @@ def design_workload(a, design: str) -> int:
     pk = peaks()
     rng = np.random.default_rng(5)
 
-    SIZES = PEPILIX_SIZES if design == "pepilix" else GIZULORN_SIZES
+    SIZES = {"pepilix": PEPILIX_SIZES, "gizulorn": GIZULORN_SIZES, "nepudra": NEPUDRA_SIZES}[design]
+    twin = "gizulorn" if design == "nepudra" else "dense"        # the model timed beside the design
 
     def configs(name):
         if design == "gizulorn":
             return gizulorn_configs(name, L, ctx)
+        if design == "nepudra":
+            return nepudra_configs(name, L, ctx)
         D, H, dn, dr, dv, r, E, top, ff, V = PEPILIX_SIZES[name]
         mixer = {"heads": H, "dim": dn, "rot_dim": dr, "vdim": dv, "kv_rank": r, "scale": (dn + dr) ** -0.5,
                  "rot": {"base": 10000.0, "dims": dr}}
@@ -539,15 +590,15 @@ def design_workload(a, design: str) -> int:
     clocks = ClockSampler()
     clocks.start()
     sizes, launches = {}, 0
-    chosen = a.sizes if design == "pepilix" or a.sizes != "w1024,w2048" else ",".join(GIZULORN_SIZES)
+    chosen = a.sizes if design == "pepilix" or a.sizes != "w1024,w2048" else ",".join(SIZES)
     for name in [n for n in chosen.split(",") if n]:
         if name not in SIZES:
             raise SystemExit(f"--sizes: {name!r} is not one of {sorted(SIZES)}")
         pep, dense = configs(name)
-        res = {design: run(pep, False), "dense": run(dense, False)}
-        launches += res[design].pop("launches", 0) + res["dense"].pop("launches", 0)
+        res = {design: run(pep, False), twin: run(dense, False)}
+        launches += res[design].pop("launches", 0) + res[twin].pop("launches", 0)
         if not a.no_points:
-            for which, cfg in ((design, pep), ("dense", dense)):
+            for which, cfg in ((design, pep), (twin, dense)):
                 prof = run(cfg, True)
                 for k in ("prefill_classes", "decode_classes"):
                     res[which][k] = [{"class": c["class"], "launches": c["launches"], "ms": c["ms"], "share": c["share"],
@@ -563,8 +614,11 @@ def design_workload(a, design: str) -> int:
         "config": {"workload": design, "layers": L, "global_batch": batch, "seq_len": ctx, "page_size": page,
                    "sizes": {n: dict(zip(("width", "heads", "dim", "rot_dim", "vdim", "kv_rank", "experts", "top", "ff", "vocab")
                                          if design == "pepilix" else
+                                         ("width", "heads", "kv_heads", "dim", "window", "delta_heads", "delta_dim", "ff", "vocab")
+                                         if design == "nepudra" else
                                          ("width", "heads", "dim", "vdim", "kv_heads", "window", "key_heads", "experts", "top", "groups",
                                           "keep", "ff", "shared_ff", "vocab"), SIZES[n])) for n in sizes},
+                   "beside": twin,
                    "weights": "random N(0,0.02)", "peaks": pk["source"], "l2": "inputs larger than L2"},
         "clocks": clk, "gpu_launches": int(launches), "sizes": sizes}))
     return 0

@@ -177,9 +177,12 @@ __device__ __forceinline__ void pair_chunk(const float* qh, const float* Ks, con
   const float* kr = Ks + lane * (dk + 1);
   float s = 0.f;
   for (int d = 0; d < dk; ++d) s = fmaf(qh[d], kr[d], s);
-  s *= scale;
-  if (softcap > 0.f) s = softcap * tanhf(s / softcap);
-  s = valid ? s : -INFINITY;
+  if (softcap > 0.f) {
+    s = softcap * tanhf(__fmul_rn(s, scale) / softcap);
+    s = valid ? s : -INFINITY;
+  } else {
+    s = valid ? s * scale : -INFINITY;
+  }
   const float mn = fmaxf(m, warp_max(s));
   if (mn == -INFINITY) return;                     // nothing seen so far, nothing here
   const float pj = valid ? expf(s - mn) : 0.f;

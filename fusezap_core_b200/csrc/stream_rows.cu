@@ -2,6 +2,7 @@
 // 32-bit; T is the dtype of a table that is read or of an activation that is written.
 #include "common.cuh"
 #include <math.h>
+#include <stdint.h>
 
 namespace {
 // x[n] += table[r], r chosen by a hash of (previous token, token). One block per row. The block of a portion's first row
@@ -38,6 +39,22 @@ hashed_pair_embed_kernel(const T* __restrict__ table, const int* __restrict__ id
   for (int d = threadIdx.x; d < D; d += blockDim.x) dst[d] += Cvt<T>::to_f(src[d]);
 }
 
+// Four neighbouring elements of sum_j coef[j] streams[j], j = 0 .. depth, plus coef[depth + 1] X: fused multiply-adds in
+// rising j from zero, element by element as the scalar loops do.
+__device__ __forceinline__ float4 averaged4(const float* __restrict__ st, int D, int d, int depth, const float* __restrict__ coef,
+                                            float4 X) {
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+  for (int j = 0; j <= depth; ++j) {
+    const float4 s = *(const float4*)(st + (size_t)j * D + d);
+    const float c = coef[j];
+    acc.x = fmaf(c, s.x, acc.x); acc.y = fmaf(c, s.y, acc.y); acc.z = fmaf(c, s.z, acc.z); acc.w = fmaf(c, s.w, acc.w);
+  }
+  const float c = coef[depth + 1];
+  acc.x = fmaf(c, X.x, acc.x); acc.y = fmaf(c, X.y, acc.y); acc.z = fmaf(c, X.z, acc.z); acc.w = fmaf(c, X.w, acc.w);
+  return acc;
+}
+
 // streams: (N, L1, D). X = x + delta; streams[n, depth + 1] = X; x = sum_j coef[j] streams[n, j], j = 0 .. depth + 1, by
 // fused multiply-adds in rising j from zero. coef null (depth -1): only X is kept and x = X.
 __global__ void __launch_bounds__(256)
@@ -49,6 +66,15 @@ depth_average_kernel(float* __restrict__ streams, int L1, int depth, const float
   float* st = streams + (size_t)n * L1 * D;
   float* xr = x + (size_t)n * D;
   const float* dr = delta != nullptr ? delta + (size_t)n * D : nullptr;
+  if ((D & 3) == 0 && ((((uintptr_t)streams) | ((uintptr_t)x) | ((uintptr_t)delta)) & 15) == 0) {      // 16 bytes per access; every element's sum is the scalar loop's
+    for (int d = 4 * threadIdx.x; d < D; d += 4 * blockDim.x) {
+      float4 X = *(const float4*)(xr + d);
+      if (dr != nullptr) { const float4 e = *(const float4*)(dr + d); X.x += e.x; X.y += e.y; X.z += e.z; X.w += e.w; }
+      *(float4*)(st + (size_t)(depth + 1) * D + d) = X;
+      *(float4*)(xr + d) = coef != nullptr ? averaged4(st, D, d, depth, coef, X) : X;
+    }
+    return;
+  }
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
     const float X = dr != nullptr ? xr[d] + dr[d] : xr[d];
     st[(size_t)(depth + 1) * D + d] = X;
@@ -90,7 +116,19 @@ depth_average_norm_kernel(float* __restrict__ streams, int L1, int depth, const 
   float* xr = x + (size_t)n * D;
   const float* dr = delta != nullptr ? delta + (size_t)n * D : nullptr;
   float ss = 0.f;
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+  const bool vec = (D & 3) == 0 && ((((uintptr_t)streams) | ((uintptr_t)x) | ((uintptr_t)delta)) & 15) == 0;
+  for (int d = 4 * threadIdx.x; vec && d < D; d += 4 * blockDim.x) {
+    float4 X = *(const float4*)(xr + d);
+    if (dr != nullptr) { const float4 e = *(const float4*)(dr + d); X.x += e.x; X.y += e.y; X.z += e.z; X.w += e.w; }
+    const float4 acc = averaged4(st, D, d, depth, coef, X);
+    if (rows == nullptr) {
+      *(float4*)(st + (size_t)(depth + 1) * D + d) = X;
+      *(float4*)(xr + d) = acc;
+    }
+    *(float4*)(avg + d) = acc;
+    ss = fmaf(acc.x, acc.x, ss); ss = fmaf(acc.y, acc.y, ss); ss = fmaf(acc.z, acc.z, ss); ss = fmaf(acc.w, acc.w, ss);
+  }
+  for (int d = threadIdx.x; !vec && d < D; d += blockDim.x) {
     const float X = dr != nullptr ? xr[d] + dr[d] : xr[d];
     float acc = 0.f;
     for (int j = 0; j <= depth; ++j) acc = fmaf(coef[j], st[(size_t)j * D + d], acc);

@@ -66,10 +66,11 @@ class SinkAttention(Mixer):
     def tensors(self) -> dict[str, ParamSpec]:
         n = self.names
         rows = {"q": self.Hq * self.dk, "k": self.Hkv * self.dk, "v": self.Hkv * self.dv, "out": self.D}
-        out = {n["q"]: ParamSpec((rows["q"], self.D)), n["out"]: ParamSpec((self.D, self.Hq * self.dv))}
+        out = {n["q"]: ParamSpec((rows["q"], self.D))}      # (declaration order is the order in which random weights are drawn)
         if self.own_kv:
             out[n["k"]] = ParamSpec((rows["k"], self.D))
             out[n["v"]] = ParamSpec((rows["v"], self.D))
+        out[n["out"]] = ParamSpec((self.D, self.Hq * self.dv))
         for x in self.bias:
             if self.own_kv or x not in ("k", "v"):
                 out[n[x] + self.bias_suffix] = ParamSpec((rows[x],), role="vector")
