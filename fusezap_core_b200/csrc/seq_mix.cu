@@ -367,21 +367,24 @@ sink_attention_merge_kernel(const AttnArgs a) {
   }
   const ChunkWalk walk(p, p, a.window, a.keep_first);
   const int runs = (walk.count + a.unit_chunks - 1) / a.unit_chunks;
-  float m = -INFINITY, l = 0.f, acc[DPL];
+  // the largest of the runs' maxima first, then every run's term with its own factor: no load waits for a sum, and the
+  // order of the sums is that of the runs, whatever else the step holds
+  const float* part = a.part + ((size_t)n * a.Hq + head) * a.max_units * (dv + 2);
+  float m = -INFINITY;
+  for (int u = lane; u < runs; u += 32) m = fmaxf(m, part[(size_t)u * (dv + 2)]);
+  m = warp_max(m);
+  float l = 0.f, acc[DPL];
 #pragma unroll
   for (int i = 0; i < DPL; ++i) acc[i] = 0.f;
+#pragma unroll 4
   for (int u = 0; u < runs; ++u) {
-    const float* o = a.part + (((size_t)n * a.Hq + head) * a.max_units + u) * (dv + 2);
-    const float mu = o[0], lu = o[1];
-    const float mn = fmaxf(m, mu);
-    if (mn == -INFINITY) continue;
-    const float ca = expf(m - mn), cb = expf(mu - mn);
-    l = l * ca + lu * cb;
-    m = mn;
+    const float* o = part + (size_t)u * (dv + 2);
+    const float cb = expf(o[0] - m);               // 0 for a run that saw no key
+    l = fmaf(o[1], cb, l);
 #pragma unroll
     for (int i = 0; i < DPL; ++i) {
       const int d = lane + 32 * i;
-      if (d < dv) acc[i] = acc[i] * ca + o[2 + d] * cb;
+      if (d < dv) acc[i] = fmaf(o[2 + d], cb, acc[i]);
     }
   }
   pair_finish<T, DPL>(a, n, head, m, l, acc);
