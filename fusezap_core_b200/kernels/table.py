@@ -125,6 +125,7 @@ class CudaOps(Ops):
         self.prefill_tcgen05 = True        # False: long portions on the mma.sync flash-attention kernel
         self.fuse_swiglu = True            # gate/up product and SwiGLU in one kernel where the sizes allow it
         self.fuse_argmax = True            # lm_head product and argmax in one pass where no logits are asked for
+        self.sink_max_runs = 64            # single-token steps over all earlier keys: a row's keys are cut into at most this many runs
         self.fuse_depth_norm = True        # the depth average of a layer's result and the norm that follows in one kernel
         self.fuse_rope = True              # q/k/v product, rotation and cache write in one kernel (few-token steps)
         # 128-row tiles for experts with hundreds of rows: measured slower for the gated product (347 against 319 us at
@@ -1038,7 +1039,7 @@ class CudaOps(Ops):
         part = None
         if self.split_decode_keys and self.dtype == torch.bfloat16 and max_portion == 1:
             ctx = max(1, int(meta.max_context))
-            unit_chunks = 2 if window else max(2, -(-ctx // (32 * 64)))
+            unit_chunks = 2 if window else max(2, -(-ctx // (32 * self.sink_max_runs)))
             units = int(self.seq.fz_sink_attention_units(c_int(window), c_int(keep_first), c_int(ctx), c_int(unit_chunks)))
             part = self._scratch("sink attention partials", n * num_heads * units * (value_dim + 2), torch.float32)
         self._check(self.seq.fz_sink_attention(

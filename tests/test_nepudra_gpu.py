@@ -298,6 +298,7 @@ def attention_rows(dtype, Hq, Hkv, dk, dv, window, cap, gated, T, portions, page
     qkv = torch.cat([q.view(T, -1), k.view(T, -1), v.view(T, -1)], 1).float()
     ops.rotate_kv_write(qkv.to(DEV), None, None, 0, 0, Meta([(T, 0, 0)], table), cache, torch.empty(T, Hq * dk, dtype=dt, device=DEV), Hq, Hkv, dk, dv)
     meta = Meta([(n, p0, 0) for n, p0 in portions], table.repeat(len(portions), 1), pad=1)
+    meta.max_portion = max(n for n, _ in portions)      # (a step of single tokens takes the kernels that cut a row's keys into runs)
     rows = [p for n, p0 in portions for p in range(p0, p0 + n)]
     qs = torch.cat([q[rows].view(len(rows), -1), torch.zeros(1, Hq * dk, dtype=dt)]).to(DEV)
     gl = torch.randn(T, Hq + 3, generator=g) * 2
