@@ -113,7 +113,7 @@ rotate_kv_write_kernel(const float* __restrict__ qkv, int ld, const float* __res
 // Two kernels with the same arithmetic per chunk: `sink_attention_tile_kernel` gives a block up to 32 pairs of
 // consecutive rows of one portion and one kv head (the rows share every key / value load); `sink_attention_unit_kernel`
 // (steps of single tokens) gives a block a run of a row's chunks and leaves (max, sum, accumulator) per run for
-// `sink_attention_merge_kernel`, which adds the runs up in rising order.
+// `sink_attention_merge_kernel`, which adds the runs up in an order that the row's number of runs fixes.
 constexpr int CHUNK = 32;
 constexpr int ATT_WARPS = 8;
 constexpr int MAX_PPW = 4;                         // pairs per warp
@@ -351,18 +351,21 @@ sink_attention_unit_kernel(const AttnArgs a) {
   }
 }
 
-// grid (rows, query heads), a warp each: the runs of a row in rising order, then the sink.
+// grid (rows, query heads), MERGE_WARPS warps each: warp w adds up the runs w, w + MERGE_WARPS, ... of a row in rising
+// order, warp 0 then adds the warps' sums in rising w; then the sink. The order depends on the row's number of runs only.
+constexpr int MERGE_WARPS = 4;
 template <typename T, int DPL>
-__global__ void __launch_bounds__(32)
+__global__ void __launch_bounds__(32 * MERGE_WARPS)
 sink_attention_merge_kernel(const AttnArgs a) {
   fz_grid_launch_dependents();
-  const int n = blockIdx.x, head = blockIdx.y, lane = threadIdx.x;
+  __shared__ float sums[MERGE_WARPS][32 * DPL + 1];
+  const int n = blockIdx.x, head = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int row = a.seq_row[n], p = a.pos[n];
   fz_grid_wait();
   const int dv = a.dv;
   if (row < 0) {
     T* o = (T*)a.out + ((size_t)n * a.Hq + head) * dv;
-    for (int d = lane; d < dv; d += 32) o[d] = Cvt<T>::from_f(0.f);
+    for (int d = threadIdx.x; d < dv; d += blockDim.x) o[d] = Cvt<T>::from_f(0.f);
     return;
   }
   const ChunkWalk walk(p, p, a.window, a.keep_first);
@@ -377,7 +380,7 @@ sink_attention_merge_kernel(const AttnArgs a) {
 #pragma unroll
   for (int i = 0; i < DPL; ++i) acc[i] = 0.f;
 #pragma unroll 4
-  for (int u = 0; u < runs; ++u) {
+  for (int u = warp; u < runs; u += MERGE_WARPS) {
     const float* o = part + (size_t)u * (dv + 2);
     const float cb = expf(o[0] - m);               // 0 for a run that saw no key
     l = fmaf(o[1], cb, l);
@@ -386,6 +389,18 @@ sink_attention_merge_kernel(const AttnArgs a) {
       const int d = lane + 32 * i;
       if (d < dv) acc[i] = fmaf(o[2 + d], cb, acc[i]);
     }
+  }
+  if (warp > 0) {
+    if (lane == 0) sums[warp][32 * DPL] = l;
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) sums[warp][lane + 32 * i] = acc[i];
+  }
+  __syncthreads();
+  if (warp > 0) return;
+  for (int w = 1; w < MERGE_WARPS; ++w) {
+    l += sums[w][32 * DPL];
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) acc[i] += sums[w][lane + 32 * i];
   }
   pair_finish<T, DPL>(a, n, head, m, l, acc);
 }
@@ -1069,7 +1084,7 @@ int launch_sink(AttnArgs a, int N, int n_seg, int max_portion, int units, cudaSt
     if (st != FZ_OK) return st;
     fz_launch(sink_attention_unit_kernel<T, DPL>, dim3(N, a.Hkv * slices, units), dim3(32 * ATT_WARPS), smem, stream, a);
     FZ_LAUNCH_CHECK();
-    fz_launch(sink_attention_merge_kernel<T, DPL>, dim3(N, a.Hq), dim3(32), 0, stream, a);
+    fz_launch(sink_attention_merge_kernel<T, DPL>, dim3(N, a.Hq), dim3(32 * MERGE_WARPS), 0, stream, a);
     FZ_LAUNCH_CHECK();
     return FZ_OK;
   }
