@@ -147,6 +147,28 @@ struct ChunkWalk {
   __device__ int chunk(int it) const { return it <= first_end ? it : c2 + (it - first_end - 1); }
 };
 
+// Sixteen bytes of T as floats.
+template <typename T> struct Vec16;
+template <> struct Vec16<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void load(const float* p, float* o) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
+  }
+};
+template <> struct Vec16<__nv_bfloat16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* o) {
+    const uint4 v = *reinterpret_cast<const uint4*>(p);
+    const unsigned w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      o[2 * i] = __uint_as_float(w[i] << 16);
+      o[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+};
+
 // All threads of the block: keys and values of chunk c of kv head `kvh` that some row of the block may see, as floats.
 template <typename T>
 __device__ __forceinline__ void load_chunk(const AttnArgs& a, const int* trow, int kvh, int c, int lo, int kept, int p_last,
@@ -154,6 +176,53 @@ __device__ __forceinline__ void load_chunk(const AttnArgs& a, const int* trow, i
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, W = blockDim.x >> 5;
   const T* kp = (const T*)a.k_pool;
   const T* vp = (const T*)a.v_pool;
+  constexpr int VN = Vec16<T>::N;
+  if (a.dk % VN == 0 && a.dv % VN == 0 && a.page_stride % VN == 0 && a.head_stride % VN == 0 && a.tok_stride % VN == 0 &&
+      (reinterpret_cast<uintptr_t>(kp) & 15) == 0 && (reinterpret_cast<uintptr_t>(vp) & 15) == 0) {
+    // 16 bytes per load: lane j of every warp finds the place of key 32c + j, the lanes that fetch a piece of that key
+    // take it from there by a shuffle; the values stored are the same as below
+    const int key = c * CHUNK + lane;
+    long long off = -1;
+    if (key <= p_last && (key >= lo || key < kept)) {
+      const int page = trow[key / a.page_size];
+      if (page < 0 || page >= a.n_pages) { if (warp == 0) atomicOr(a.err, FZ_ERR_NO_PAGE); }
+      else off = (long long)page * a.page_stride + (long long)kvh * a.head_stride + (long long)(key % a.page_size) * a.tok_stride;
+    }
+    const int lk = a.dk / VN, lv = a.dv / VN;
+    for (int base = warp * 32; base < CHUNK * lk; base += 32 * W) {
+      const int e = base + lane;
+      const bool in = e < CHUNK * lk;
+      const int j = in ? e / lk : 0, x = e - j * lk;
+      const long long oj = __shfl_sync(0xffffffffu, off, j);
+      if (!in) continue;
+      float v[VN];
+      if (oj >= 0) Vec16<T>::load(kp + oj + x * VN, v);
+      else {
+#pragma unroll
+        for (int t = 0; t < VN; ++t) v[t] = 0.f;
+      }
+      float* dst = Ks + j * (a.dk + 1) + x * VN;
+#pragma unroll
+      for (int t = 0; t < VN; ++t) dst[t] = v[t];
+    }
+    for (int base = warp * 32; base < CHUNK * lv; base += 32 * W) {
+      const int e = base + lane;
+      const bool in = e < CHUNK * lv;
+      const int j = in ? e / lv : 0, x = e - j * lv;
+      const long long oj = __shfl_sync(0xffffffffu, off, j);
+      if (!in) continue;
+      float v[VN];
+      if (oj >= 0) Vec16<T>::load(vp + oj + x * VN, v);
+      else {
+#pragma unroll
+        for (int t = 0; t < VN; ++t) v[t] = 0.f;
+      }
+      float4* dst = reinterpret_cast<float4*>(Vs + j * a.dv + x * VN);
+#pragma unroll
+      for (int t = 0; t < VN / 4; ++t) dst[t] = make_float4(v[4 * t], v[4 * t + 1], v[4 * t + 2], v[4 * t + 3]);
+    }
+    return;
+  }
   for (int j = warp; j < CHUNK; j += W) {
     const int key = c * CHUNK + j;
     long long off = -1;
