@@ -90,6 +90,7 @@ def test_long_decoding_through_windows_temperature_periods_and_page_borders(dirs
 import plain_nepudra as plain
 from fusezap_core_b200.cache import KVNeed
 from fusezap_core_b200.kernels import cuda_ops
+from fusezap_core_b200.parts import LayerCache
 from test_gizulorn_gpu import DEV, DT, F, Meta, close, paged, scan_portions, shuffled_tables
 
 
@@ -360,6 +361,47 @@ def test_a_loud_key_is_seen_exactly_where_the_mask_says(dtype, as_portion, dk, d
                 if p >= j:
                     assert same == sees, (j, p, sees)
                 at += 1
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("Hq,Hkv,dk,dv,window", [(4, 2, 64, 64, 0), (6, 3, 32, 96, 37), (2, 1, 128, 128, 0), (4, 1, 24, 40, 20)])
+def test_wide_and_narrow_loads_of_the_cache_give_the_same_bits(dtype, Hq, Hkv, dk, dv, window):
+    """The attention kernels read keys and values 16 bytes at a time where sizes, strides and addresses allow it and
+    element by element otherwise. The same pages in a pool whose first element lies at an odd address take the narrow
+    path: portions and single tokens leave the same bits on both."""
+    ops, g, page, B, T = cuda_ops(dtype), torch.Generator().manual_seed(dk + dv), 8, 3, 150
+    per = -(-T // page)
+    need = KVNeed(Hkv, dk, 0, value_dim=dv)
+    shape = need.pool_shape(1, B * per + 2, page)
+    count = 1
+    for x in shape:
+        count *= x
+    even = torch.randn(count, generator=g).to(DT[dtype]).to(DEV)
+    shifted = torch.zeros(count + 8, dtype=DT[dtype], device=DEV)
+    shifted[1: 1 + count] = even
+    caches = []
+    for flat in (even, shifted[1: 1 + count]):
+        keys, values = need.views(flat.view(shape)[0])
+        caches.append(LayerCache(keys, values, 0, page, True, {}))
+    assert caches[0].keys.data_ptr() % 16 == 0 and caches[1].keys.data_ptr() % 16 != 0
+    tables = shuffled_tables(B, per, B * per + 2, 5)
+    for portions in ([(40, T - 40, 0), (1, T - 1, 1), (17, 60, 2)], [(1, T - 1, 0), (1, 77, 1), (1, 8, 2)]):
+        meta = Meta(portions, tables, pad=1)
+        meta.max_portion = max(n for n, _, _ in portions)
+        n = meta.n_rows
+        q = torch.randn(n, Hq * dk, generator=g).to(DT[dtype]).to(DEV)
+        gate = torch.randn(n, Hq, generator=g).to(DEV)
+        outs = []
+        for cache in caches:
+            out = torch.empty(n, Hq * dv, dtype=DT[dtype], device=DEV)
+            before, ops.sink_tensor_cores = ops.sink_tensor_cores, False     # (the tensor-core kernel takes aligned pools only)
+            try:
+                ops.sink_attention(q, cache, meta, out, Hq, Hkv, dk, dv, 0.2, window, 0, None, softcap=9.0, gate=(gate, 0))
+            finally:
+                ops.sink_tensor_cores = before
+            ops.check_errors()
+            outs.append(out)
+        assert torch.equal(outs[0], outs[1]), portions
 
 
 # ------------------------------------------------------------------------------------------------ the model, further
