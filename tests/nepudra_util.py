@@ -98,6 +98,40 @@ def drawn_config(seed: int) -> dict:
             "layers": layers}
 
 
+def drawn_model_config(seed: int) -> dict:
+    """A configuration of a small model's size drawn from a seed: widths of a few hundred that are and are not multiples
+    of 64, head sizes from 32 to 128 (equal and unequal for keys and values, the tensor-core kernels' 64 and 128 among
+    them), groups of 1 to 6 query heads, windows of tens to hundreds of tokens, every layer type at least once."""
+    rng = np.random.default_rng(5000 + seed)
+    pick = lambda *xs: xs[int(rng.integers(len(xs)))]
+    kinds = ["attention", "attention_2", "general_delta"] + [pick("attention", "attention_2", "general_delta")
+                                                             for _ in range(int(rng.integers(1, 4)))]
+    rng.shuffle(kinds)
+    layers, owners = [], []
+    for i, kind in enumerate(kinds):
+        ff = int(pick(0, 128, 200, 384))
+        if kind == "general_delta":
+            layers.append(_layer(kind, {"heads": int(pick(1, 2, 5, 8)), "dim": int(pick(16, 32, 64, 80, 128))}, ff))
+        elif kind == "attention_2":
+            kv, dk = int(pick(1, 2, 3)), int(pick(32, 48, 64, 80, 112, 128))
+            scaling = pick(None, (8.0, 1024, 16.0, 2.0), (2.0, 128, 8.0, 0.5), (16.0, 4096, 32.0, 1.0))
+            layers.append(_layer(kind, _att2(kv * int(pick(1, 2, 3)), kv, dk, int(pick(dk, dk, 32, 64, 128)), float(pick(dk ** -0.5, 0.08)),
+                                             int(pick(17, 64, 100, 128, 200)), float(pick(10000.0, 1e6)), int(pick(dk, dk // 2, 16)), scaling), ff))
+        elif owners and rng.random() < 0.7:
+            j = int(pick(*owners))
+            layers.append(_layer(kind, dict(layers[j]["mixer"], scale=float(pick(0.08, 0.12)), softcap=float(pick(5.0, 30.0)),
+                                            q_temp={"coef": float(pick(0.1, 1.0)), "every": int(pick(64, 100))}, kv_from=j), ff))
+        else:
+            kv, dk = int(pick(1, 2, 4)), int(pick(32, 48, 64, 80, 112, 128))
+            owners.append(i)
+            layers.append(_layer(kind, _att(kv * int(pick(1, 2, 6)), kv, dk, int(pick(dk, dk, 32, 64, 128)), float(pick(dk ** -0.5, 0.08)),
+                                            float(pick(0.1, 1.0)), int(pick(64, 100, 512)), float(pick(5.0, 30.0, 50.0))), ff))
+    return {"architecture": "Nepudra", "vocab": int(pick(300, 512, 777)), "width": int(pick(192, 200, 256, 264, 384)),
+            "norm": {"eps": float(pick(1e-6, 1e-5))},
+            "embedding": {"bigram": {"buckets": int(pick(509, 4093)), "mul_prev": int(pick(37, 1000003)), "mul_cur": int(pick(13, 999983))}},
+            "layers": layers}
+
+
 def make_dir(name: str, tmp, cfg: dict | None = None, seed: int | None = None, change=None) -> tuple[str, dict, dict]:
     """Writes configuration `name` with seeded random weights (float32); `change(tensors)` may edit them before they
     are written. Returns (folder, config, weights by name)."""

@@ -4,7 +4,7 @@ import numpy as np
 import pytest
 import torch
 
-from nepudra_util import CONFIGS, drawn_config, make_dir, plain_logits, rounded, tokens_for
+from nepudra_util import CONFIGS, drawn_config, drawn_model_config, make_dir, plain_logits, rounded, tokens_for
 from pepilix_util import run_cut, run_mixed
 from fusezap_core_b200.cache import CacheManager
 from fusezap_core_b200.engine import StepRunner, load_model
@@ -451,3 +451,28 @@ def test_configurations_drawn_at_random(seed, tmp_path):
             got = run_cut(runner, cache, "r", toks, cuts)
             model.ops.check_errors()
             agrees(got, ref, dtype, (seed, dtype, cuts, json.dumps(cfg)[:600]))
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_configurations_of_a_small_models_size(seed, tmp_path):
+    """Widths of a few hundred, head sizes up to 128, prompts of hundreds of tokens in a pool that holds the live requests
+    only: whole, with a decoded tail, in portions down to two tokens, and beside other requests, in both dtypes."""
+    import json
+    cfg = drawn_model_config(seed)
+    d, cfg, w = make_dir(f"model{seed}", tmp_path, cfg, seed)
+    L = (421, 700, 333, 1000)[seed]
+    toks, *others = tokens_for(cfg, (L, 1, 23, 97), seed=seed)
+    for dtype in ("float32", "bfloat16"):
+        need = sum(-(-len(t) // 64) * 64 for t in [toks] + others)
+        model, cache, runner = engine_parts(d, dtype, page=16, pages=need // 16, slots=4, max_len=1024)
+        refs = [oracle(cfg, w, t, dtype) for t in [toks] + others]
+        what = (seed, dtype, json.dumps(cfg)[:600])
+        for cuts in ((L,), (L - 40,) + (1,) * 40, (5, 64, 2, 33, 128, 7, 1, 1, 100, 2, 16, 17)):
+            agrees(run_cut(runner, cache, "r", toks, cuts), refs[0], dtype, what + (cuts[:3],))
+            model.ops.check_errors()
+        plan = [[("a", 200), ("b", 1)], [("a", 3), ("c", 20)], [("a", 1), ("c", 1), ("d", 50)], [("a", 64), ("c", 2), ("d", 2)],
+                [("a", 1), ("d", 45)]] + [[("a", 1)]] * 6 + [[("a", 2000)]]
+        got = run_mixed(runner, cache, dict(zip("abcd", [toks] + others)), plan)
+        model.ops.check_errors()
+        for r, ref in zip("acd", (refs[0], refs[2], refs[3])):
+            agrees(got[r], ref, dtype, what + (r,))
