@@ -60,6 +60,15 @@ def _nepudra(c: dict):
 register_architecture("Nepudra", _nepudra)
 
 
+def _gimotar(c: dict):
+    from .gimotar import GimotarConfig
+    cfg = GimotarConfig.from_json(c)
+    return cfg, cfg.spec()
+
+
+register_architecture("Gimotar", _gimotar)
+
+
 def read_config_json(model_dir: str) -> dict:
     path = os.path.join(model_dir, "config.json")
     if not os.path.isfile(path):

@@ -4,6 +4,8 @@
 //
 //   e_j: the cached vector of key j (W values); scores s_j = (q[n, h] . e_j) * scale over the keys
 //   max(0, p - window + 1) <= j <= p of the row's own request (window 0: all); out[n, h] = softmax(s) . e[:, :Wv]
+//   with `sink` (one float32 per head): the softmax's denominator also holds exp(sink[h]), which has no value; it
+//   enters after the last chunk.
 //
 // One block per (token row, slice of up to 32 heads); warp w serves heads w, w + W, ... of the slice, so they share every
 // load of a key. Keys are walked in chunks of 32 whose boundaries are multiples of 32 in absolute position: lane j scores
@@ -23,7 +25,7 @@ template <typename T, int DPL>   // DPL: output values per lane = ceil(Wv / 32)
 __global__ void attn_latent_kernel(const T* __restrict__ q, const T* __restrict__ pool, const int* __restrict__ pos,
                                    const int* __restrict__ seq_row, const int* __restrict__ table, int mb,
                                    long long page_stride, int page_size, int num_pages, T* __restrict__ out, int H, int W,
-                                   int Wv, float scale, int window, int slice, int* err) {
+                                   int Wv, float scale, int window, int slice, int* err, const float* __restrict__ sink) {
   fz_grid_launch_dependents();
   fz_grid_wait();
   extern __shared__ float smem[];
@@ -99,11 +101,17 @@ __global__ void attn_latent_kernel(const T* __restrict__ q, const T* __restrict_
   for (int a = 0; a < MAX_HPW; ++a) {
     const int g = warp + a * NW;
     if (g >= G) break;
+    float corr = 1.f;
+    if (sink != nullptr) {
+      const float sk = sink[h0 + g], mn = fmaxf(m[a], sk);
+      corr = expf(m[a] - mn);
+      l[a] = l[a] * corr + expf(sk - mn);
+    }
     const float inv = 1.0f / l[a];
 #pragma unroll
     for (int i = 0; i < DPL; ++i) {
       const int d = lane + 32 * i;
-      if (d < Wv) orow[g * Wv + d] = Cvt<T>::from_f(acc[a][i] * inv);
+      if (d < Wv) orow[g * Wv + d] = Cvt<T>::from_f(acc[a][i] * corr * inv);
     }
   }
 }
@@ -111,7 +119,7 @@ __global__ void attn_latent_kernel(const T* __restrict__ q, const T* __restrict_
 template <typename T, int DPL>
 int launch(const void* q, const void* pool, const int* pos, const int* seq_row, const int* table, int mb,
            long long page_stride, int page_size, int num_pages, void* out, int N, int H, int W, int Wv, float scale,
-           int window, int* err, cudaStream_t stream) {
+           int window, const float* sink, int* err, cudaStream_t stream) {
   // heads per block: as many as share a chunk of keys in shared memory (fewer for very wide cached vectors)
   int G = H < MAX_SLICE ? H : MAX_SLICE;
   while (G > 1 && sizeof(float) * ((size_t)CHUNK * (W + 1) + (size_t)G * W) > 200 * 1024) G = (G + 1) / 2;
@@ -126,7 +134,7 @@ int launch(const void* q, const void* pool, const int* pos, const int* seq_row, 
     allowed = smem;
   }
   fz_launch(kern, dim3(N, (H + G - 1) / G), dim3(32 * NW), smem, stream, (const T*)q, (const T*)pool, pos,
-            seq_row, table, mb, page_stride, page_size, num_pages, (T*)out, H, W, Wv, scale, window, G, err);
+            seq_row, table, mb, page_stride, page_size, num_pages, (T*)out, H, W, Wv, scale, window, G, err, sink);
   FZ_LAUNCH_CHECK();
   return FZ_OK;
 }
@@ -134,8 +142,8 @@ int launch(const void* q, const void* pool, const int* pos, const int* seq_row, 
 template <typename T>
 int dispatch(const void* q, const void* pool, const int* pos, const int* seq_row, const int* table, int mb,
              long long page_stride, int page_size, int num_pages, void* out, int N, int H, int W, int Wv, float scale,
-             int window, int* err, cudaStream_t stream) {
-#define FZ_GO(D) return launch<T, D>(q, pool, pos, seq_row, table, mb, page_stride, page_size, num_pages, out, N, H, W, Wv, scale, window, err, stream)
+             int window, const float* sink, int* err, cudaStream_t stream) {
+#define FZ_GO(D) return launch<T, D>(q, pool, pos, seq_row, table, mb, page_stride, page_size, num_pages, out, N, H, W, Wv, scale, window, sink, err, stream)
   const int dpl = (Wv + 31) / 32;
   if (dpl <= 1) FZ_GO(1);
   if (dpl <= 2) FZ_GO(2);
@@ -156,13 +164,13 @@ FZ_API int fz_attn_latent_check(int H, int W, int Wv) {
 
 FZ_API int fz_attn_latent(const void* q, const void* pool, const int* pos, const int* seq_row, const int* table, int mb,
                           long long page_stride, int page_size, int num_pages, void* out, int dtype, int N, int H, int W,
-                          int Wv, float scale, int window, int* err, cudaStream_t stream) {
+                          int Wv, float scale, int window, const float* sink, int* err, cudaStream_t stream) {
   if (N <= 0) return FZ_OK;
   if (fz_attn_latent_check(H, W, Wv) != FZ_OK || page_size <= 0) return FZ_BAD_SHAPE;
   if (dtype == FZ_F32)
-    return dispatch<float>(q, pool, pos, seq_row, table, mb, page_stride, page_size, num_pages, out, N, H, W, Wv, scale, window, err, stream);
+    return dispatch<float>(q, pool, pos, seq_row, table, mb, page_stride, page_size, num_pages, out, N, H, W, Wv, scale, window, sink, err, stream);
   if (dtype == FZ_BF16)
-    return dispatch<__nv_bfloat16>(q, pool, pos, seq_row, table, mb, page_stride, page_size, num_pages, out, N, H, W, Wv, scale, window, err, stream);
+    return dispatch<__nv_bfloat16>(q, pool, pos, seq_row, table, mb, page_stride, page_size, num_pages, out, N, H, W, Wv, scale, window, sink, err, stream);
   return FZ_BAD_DTYPE;
 }
 

@@ -10,6 +10,9 @@
 // Wv / 8 accumulators. mma.sync m16n8k16, float32 scores, online softmax in the exp2 domain with float32 max and sum.
 // Key tiles start at multiples of BN in absolute position, so a row's sums do not depend on how the prompt was cut.
 //
+// With `sink` (one float32 per head) the denominator of pair p, head p % H, also holds exp(sink): it enters once, in the
+// epilogue, or in the merge kernel where the keys were cut into ranges.
+//
 // Sizes: W % 16 == 0, W <= 1024; value width Wv <= W, padded to a multiple of 32 that still fits in W (the padded
 // columns are computed and not stored). Everything else goes to the general kernel.
 #include "attn_mma.cuh"
@@ -59,7 +62,7 @@ attn_latent_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* 
                       const int* __restrict__ seg, int n_seg, const int* __restrict__ table, int mb,
                       long long page_stride, int page_size, int num_pages, __nv_bfloat16* __restrict__ out, int H, int W,
                       int Wv, float scale_log2, int window, float* __restrict__ part_o, float* __restrict__ part_ml,
-                      int split_keys, int* err) {
+                      int split_keys, int* err, const float* __restrict__ sink) {
   fz_grid_launch_dependents();
   fz_grid_wait();
   constexpr int NBS = BN / 16;                 // 8-key blocks of S per warp (half the tile's keys)
@@ -269,7 +272,14 @@ attn_latent_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* 
   for (int hh = 0; hh < 2; ++hh) {
     const int r = r_lo + 8 * hh;
     if (r >= valid) continue;
-    const float inv = 1.0f / (red[r] + red[BM + r]);
+    float inv = red[r] + red[BM + r];
+    if (sink != nullptr) {      // (in the exp2 domain, like the scores)
+      const float sk = sink[(pair0 + r) % H] * 1.4426950408889634f, mn = fmaxf(m_run[hh], sk);
+      const float corr = exp2f(m_run[hh] - mn);
+      inv = corr / (inv * corr + exp2f(sk - mn));
+    } else {
+      inv = 1.0f / inv;
+    }
     __nv_bfloat16* orow = out + ((size_t)row0 * H + pair0 + r) * Wv;
 #pragma unroll
     for (int i = 0; i < 2 * NV16; ++i) {
@@ -285,7 +295,7 @@ attn_latent_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* 
 // columns with independent loads. n_split <= 32.
 __global__ void __launch_bounds__(256)
 attn_latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const int* __restrict__ seg,
-                         int n_seg, int n_split, __nv_bfloat16* __restrict__ out, int H, int Wv) {
+                         int n_seg, int n_split, __nv_bfloat16* __restrict__ out, int H, int Wv, const float* __restrict__ sink) {
   fz_grid_launch_dependents();
   fz_grid_wait();
   __shared__ float w_s[32];
@@ -301,7 +311,8 @@ attn_latent_merge_kernel(const float* __restrict__ part_o, const float* __restri
     const int y = threadIdx.x;
     const float my = y < n_split ? part_ml[((base + y) * BM + r) * 2] : -INFINITY;
     const float ly = y < n_split ? part_ml[((base + y) * BM + r) * 2 + 1] : 0.f;
-    const float m = warp_max(my);
+    const float sk = sink != nullptr ? sink[(pair0 + r) % H] * 1.4426950408889634f : -INFINITY;
+    const float m = fmaxf(warp_max(my), sk);
     const float w = ly > 0.f ? exp2f(my - m) : 0.f;      // an empty range has sum 0 (its partial output was never written)
     float l = ly * w;
 #pragma unroll
@@ -310,7 +321,7 @@ attn_latent_merge_kernel(const float* __restrict__ part_o, const float* __restri
       if (y >= o) l += up;
     }
     w_s[y] = w;                                            // (0 for the lanes beyond the ranges)
-    if (y == 31) inv_s = 1.0f / l;
+    if (y == 31) inv_s = 1.0f / (sink != nullptr ? l + exp2f(sk - m) : l);
   }
   __syncthreads();
   for (int c = threadIdx.x; c < Wv; c += blockDim.x) {
@@ -342,7 +353,7 @@ size_t smem_bytes(int W, int bn) {
 template <int NV16, int BN>
 int launch(const void* q, const void* pool, const int* seg, int n_seg, const int* table, int mb, long long page_stride,
            int page_size, int num_pages, void* out, int blocks, int H, int W, int Wv, float scale, int window,
-           float* part_o, float* part_ml, int n_split, int split_keys, int* err, cudaStream_t stream) {
+           float* part_o, float* part_ml, int n_split, int split_keys, const float* sink, int* err, cudaStream_t stream) {
   const size_t smem = smem_bytes(W, BN);
   auto kern = attn_latent_tc_kernel<NV16, BN>;
   static size_t allowed = 48 * 1024;
@@ -353,11 +364,11 @@ int launch(const void* q, const void* pool, const int* seg, int n_seg, const int
   }
   fz_launch(kern, dim3(blocks, n_split), dim3(THREADS), smem, stream, (const __nv_bfloat16*)q, (const __nv_bfloat16*)pool, seg,
             n_seg, table, mb, page_stride, page_size, num_pages, (__nv_bfloat16*)out, H, W, Wv, scale * 1.4426950408889634f,
-            window, part_o, part_ml, split_keys, err);
+            window, part_o, part_ml, split_keys, err, sink);
   FZ_LAUNCH_CHECK();
   if (split_keys > 0) {
     fz_launch(attn_latent_merge_kernel, dim3(blocks, BM), dim3(256), 0, stream, (const float*)part_o, (const float*)part_ml, seg,
-              n_seg, n_split, (__nv_bfloat16*)out, H, Wv);
+              n_seg, n_split, (__nv_bfloat16*)out, H, Wv, sink);
     FZ_LAUNCH_CHECK();
   }
   return FZ_OK;
@@ -401,7 +412,7 @@ FZ_API long long fz_attn_latent_tc_scratch(int blocks, int n_split, int Wv) {
 FZ_API int fz_attn_latent_tc(const void* q, const void* pool, const int* seq_row, const int* seg, int n_seg,
                              const int* table, int mb, long long page_stride, int page_size, int num_pages, void* out,
                              int N, int blocks, int H, int W, int Wv, float scale, int window, int n_split,
-                             int max_context, float* scratch, int* err, cudaStream_t stream) {
+                             int max_context, float* scratch, const float* sink, int* err, cudaStream_t stream) {
   if (N <= 0) return FZ_OK;
   if (fz_attn_latent_tc_check(H, W, Wv) != FZ_OK || page_size <= 0) return FZ_BAD_SHAPE;
   if (n_split < 1 || n_split > 65535 || (n_split > 1 && scratch == nullptr)) return FZ_BAD_SHAPE;
@@ -412,8 +423,8 @@ FZ_API int fz_attn_latent_tc(const void* q, const void* pool, const int* seq_row
   FZ_LAUNCH_CHECK();
   if (blocks <= 0 || n_seg <= 0) return FZ_OK;
   const bool wide = smem_bytes(W, 64) <= 200 * 1024;
-#define FZ_GO(NV) return wide ? launch<NV, 64>(q, pool, seg, n_seg, table, mb, page_stride, page_size, num_pages, out, blocks, H, W, Wv, scale, window, part_o, part_ml, n_split, split_keys, err, stream) \
-                              : launch<NV, 32>(q, pool, seg, n_seg, table, mb, page_stride, page_size, num_pages, out, blocks, H, W, Wv, scale, window, part_o, part_ml, n_split, split_keys, err, stream)
+#define FZ_GO(NV) return wide ? launch<NV, 64>(q, pool, seg, n_seg, table, mb, page_stride, page_size, num_pages, out, blocks, H, W, Wv, scale, window, part_o, part_ml, n_split, split_keys, sink, err, stream) \
+                              : launch<NV, 32>(q, pool, seg, n_seg, table, mb, page_stride, page_size, num_pages, out, blocks, H, W, Wv, scale, window, part_o, part_ml, n_split, split_keys, sink, err, stream)
   switch (nv16_for(Wv)) {
     case 1: FZ_GO(1);
     case 2: FZ_GO(2);

@@ -25,7 +25,7 @@ sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
                           long long head_stride, long long tok_stride, int page_size, int n_pages,
                           __nv_bfloat16* __restrict__ out, int Hq, int Hkv, float scale_log2, int window, int keep_first,
                           const float* __restrict__ sink, float cap_log2, float over_cap, const float* __restrict__ gate,
-                          int gate_ld, int gate_off, int N, int* err) {
+                          int gate_ld, int gate_off, int N, int* err, int span) {
   fz_grid_launch_dependents();
   fz_grid_wait();
   constexpr int KSTEPS = HD / 16, NB = HD / 8, TILE_BYTES = BN * HD * 2;
@@ -48,7 +48,8 @@ sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
   const int valid_rows = min(BM, n_rows - r_off);
   const int qpos0 = pos0 + r_off;                               // position of the tile's first row
   const int last_pos = qpos0 + valid_rows - 1;
-  const int lo_tile = window > 0 ? max(0, qpos0 - window + 1) : 0;
+  // (span > 0, a chunked mask: a row also sees nothing before the start of its own block of `span` positions)
+  const int lo_tile = max(window > 0 ? max(0, qpos0 - window + 1) : 0, span > 0 ? qpos0 - qpos0 % span : 0);
   const int kept = window > 0 ? min(keep_first, lo_tile) : 0;   // keys 0 .. kept-1 are seen although they lie before the window
   const int first_end = kept > 0 ? (kept - 1) / BN : -1;        // last key tile of the kept tokens
   const int c2 = max(lo_tile / BN, first_end + 1);              // first key tile of the window not yet walked
@@ -107,7 +108,8 @@ sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
     // a warp whose rows all lie before this key tile, or whose windows all ended before it (and that is not a tile of
     // kept tokens), has nothing to do here
     const bool active = warp * 16 < valid_rows && key0 <= warp_last &&
-                        (window <= 0 || key0 + BN - 1 >= warp_first - window + 1 || key0 < keep_first);
+                        (window <= 0 || key0 + BN - 1 >= warp_first - window + 1 || key0 < keep_first) &&
+                        (span <= 0 || key0 + BN - 1 >= warp_first - warp_first % span);
     if (active) {
       const uint32_t sk = s_base + (t & 1) * 2 * TILE_BYTES, sv = sk + TILE_BYTES;
       float s[BN / 8][4];
@@ -131,7 +133,8 @@ sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
         for (int e = 0; e < 4; ++e) {
           const int key = key0 + 8 * j + 2 * (lane & 3) + (e & 1);
           const int qpos = qp[e >> 1];
-          const bool ok = key <= qpos && (window <= 0 || key >= qpos - window + 1 || key < keep_first);
+          const bool ok = key <= qpos && (window <= 0 || key >= qpos - window + 1 || key < keep_first) &&
+                          (span <= 0 || key >= qpos - qpos % span);
           // (a cap c > 0: the scaled score x becomes c tanh(x / c); cap_log2 = c log2(e), over_cap = scale / c)
           const float x = cap_log2 > 0.f ? cap_log2 * tanhf(s[j][e] * over_cap) : s[j][e] * scale_log2;
           const float v = ok ? x : -INFINITY;
@@ -209,7 +212,7 @@ template <int HD>
 int launch(const void* q, const void* k_pool, const void* v_pool, const int* seg, const int* seq_row, int n_seg, int max_portion,
            const int* table, int mb, long long page_stride, long long head_stride, long long tok_stride, int page_size,
            int n_pages, void* out, int N, int Hq, int Hkv, float scale, int window, int keep_first, const float* sink,
-           float softcap, const float* gate, int gate_ld, int gate_off, int* err, cudaStream_t stream) {
+           float softcap, const float* gate, int gate_ld, int gate_off, int span, int* err, cudaStream_t stream) {
   constexpr size_t smem = 4 * (BN * HD * 2) + BM * HD * 2;
   static bool raised = false;
   if (smem > 48 * 1024 && !raised) {
@@ -222,7 +225,8 @@ int launch(const void* q, const void* k_pool, const void* v_pool, const int* seg
   fz_launch(sink_attention_mma_kernel<HD>, dim3(n_seg + 1, tiles, Hq), dim3(THREADS), smem, stream, (const __nv_bfloat16*)q,
             (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, seg, seq_row, table, mb, page_stride, head_stride,
             tok_stride, page_size, n_pages, (__nv_bfloat16*)out, Hq, Hkv, scale * LOG2E, window, keep_first, sink,
-            softcap > 0.f ? softcap * LOG2E : 0.f, softcap > 0.f ? scale / softcap : 0.f, gate, gate_ld, gate_off, N, err);
+            softcap > 0.f ? softcap * LOG2E : 0.f, softcap > 0.f ? scale / softcap : 0.f, gate, gate_ld, gate_off, N, err,
+            span);
   FZ_LAUNCH_CHECK();
   return FZ_OK;
 }
@@ -240,16 +244,18 @@ FZ_API int fz_sink_attention_mma(const void* q, const void* k_pool, const void* 
                                  int n_seg, int max_portion, const int* table, int mb, long long page_stride,
                                  long long head_stride, long long tok_stride, int page_size, int n_pages, void* out, int N,
                                  int Hq, int Hkv, int hd, float scale, int window, int keep_first, const float* sink,
-                                 float softcap, const float* gate, int gate_ld, int gate_off, int* err, cudaStream_t stream) {
+                                 float softcap, const float* gate, int gate_ld, int gate_off, int span, int* err,
+                                 cudaStream_t stream) {
   if (N <= 0 || n_seg <= 0) return FZ_OK;
+  if (span < 0 || (span > 0 && keep_first > 0)) return FZ_BAD_SHAPE;
   if (softcap < 0.f || (gate != nullptr && (gate_off < 0 || gate_off + Hq > gate_ld))) return FZ_BAD_SHAPE;
   if (fz_sink_attention_mma_check(Hq, Hkv, hd, hd, k_pool, v_pool, page_stride, head_stride, tok_stride) != FZ_OK ||
       page_size <= 0 || max_portion <= 0 || window < 0 || keep_first < 0 || ((uintptr_t)q & 15)) return FZ_BAD_SHAPE;
   if (hd == 64)
     return launch<64>(q, k_pool, v_pool, seg, seq_row, n_seg, max_portion, table, mb, page_stride, head_stride, tok_stride,
-                      page_size, n_pages, out, N, Hq, Hkv, scale, window, keep_first, sink, softcap, gate, gate_ld, gate_off, err, stream);
+                      page_size, n_pages, out, N, Hq, Hkv, scale, window, keep_first, sink, softcap, gate, gate_ld, gate_off, span, err, stream);
   return launch<128>(q, k_pool, v_pool, seg, seq_row, n_seg, max_portion, table, mb, page_stride, head_stride, tok_stride,
-                     page_size, n_pages, out, N, Hq, Hkv, scale, window, keep_first, sink, softcap, gate, gate_ld, gate_off, err, stream);
+                     page_size, n_pages, out, N, Hq, Hkv, scale, window, keep_first, sink, softcap, gate, gate_ld, gate_off, span, err, stream);
 }
 
 #ifdef FZ_TIMELINE

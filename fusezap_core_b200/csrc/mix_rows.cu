@@ -179,7 +179,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 short_conv_kernel(const T* __restrict__ h, const T* __restrict__ w, const float* __restrict__ state,
                   const int* __restrict__ seg, const int* __restrict__ seq_row, T* __restrict__ out, int C, int taps,
-                  int residual, int act) {
+                  int residual, int act, const float* __restrict__ bias) {
   fz_grid_launch_dependents();
   fz_grid_wait();
   const int n = blockIdx.x;
@@ -203,6 +203,7 @@ short_conv_kernel(const T* __restrict__ h, const T* __restrict__ w, const float*
       else if (st != nullptr) v = st[(size_t)(taps - 1 + k) * C + c];
       acc = fmaf(Cvt<T>::to_f(w[(size_t)c * taps + j]), v, acc);
     }
+    if (bias != nullptr) acc += bias[c];
     if (residual) acc += Cvt<T>::to_f(h[(size_t)n * C + c]);
     if (act) acc = acc * (1.0f / (1.0f + expf(-acc)));      // silu of the 32-bit sum
     orow[c] = Cvt<T>::from_f(acc);
@@ -238,7 +239,7 @@ template <typename T, int TAPS>
 __global__ void __launch_bounds__(128)
 short_conv_vec_kernel(const T* __restrict__ h, const T* __restrict__ w, const float* __restrict__ state,
                       const int* __restrict__ seg, const int* __restrict__ seq_row, T* __restrict__ out, int C, int taps,
-                      int residual, int act) {
+                      int residual, int act, const float* __restrict__ bias) {
   fz_grid_launch_dependents();
   fz_grid_wait();
   const int n = blockIdx.x;
@@ -274,6 +275,12 @@ short_conv_vec_kernel(const T* __restrict__ h, const T* __restrict__ w, const fl
 #pragma unroll
         for (int e = 0; e < 8; ++e) acc[e] = fmaf(Cvt<T>::to_f(w[(size_t)(c0 + e) * taps + j]), v[e], acc[e]);
       }
+    }
+    if (bias != nullptr) {
+      float v[8];
+      ld8(bias + c0, v);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += v[e];
     }
     if (residual) {
       float v[8];
@@ -353,6 +360,13 @@ __global__ void select_tokens_kernel(const int* __restrict__ tokens, const int* 
   if (n < N) out[n] = src[n] >= 0 ? prev_ids[src[n]] : tokens[n];
 }
 
+// Which dimension d of a rotated vector is turned with, the pair's index in the tables, and whether d is the pair's first
+// member. pairing 0: d with d + half; 1: 2i with 2i + 1.
+__device__ __forceinline__ void rot_pair_of(int d, int half, int pairing, int& partner, int& pair, bool& first) {
+  if (pairing == 0) { first = d < half; partner = first ? d + half : d - half; pair = first ? d : d - half; }
+  else { first = (d & 1) == 0; partner = d ^ 1; pair = d >> 1; }
+}
+
 // ------------------------------------------------------------------------------------------------ latent cache entry
 // down: (N, L + R) float32. The row's cache entry = [w * down[:L] / rms(down[:L]) | turn(down[L:])], rounded once, stored
 // at the row's place in its pages. pool: (pages, page_size, L + R).
@@ -362,7 +376,7 @@ latent_cache_write_kernel(const float* __restrict__ down, const TW* __restrict__
                           const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rotated,
                           const int* __restrict__ pos, const int* __restrict__ seq_row, const int* __restrict__ table,
                           int mb, T* __restrict__ pool, long long page_stride, int page_size, int L, int R, int max_len,
-                          int num_pages, int* err) {
+                          int num_pages, int* err, int pairing) {
   fz_grid_launch_dependents();
   fz_grid_wait();
   __shared__ float scratch[32];
@@ -391,14 +405,14 @@ latent_cache_write_kernel(const float* __restrict__ down, const TW* __restrict__
   const float* sr = sin_t + (size_t)p * half;
   for (int d = threadIdx.x; d < R; d += blockDim.x) {
     float v = in[L + d];
-    if (d < half) {
+    if (d < rotated) {
+      int partner, pair;
+      bool first;
+      rot_pair_of(d, half, pairing, partner, pair, first);
+      const float other = in[L + partner];
       float o1, o2;
-      fz_rope_pair(v, in[L + d + half], cr[d], sr[d], o1, o2);
-      v = o1;
-    } else if (d < rotated) {
-      float o1, o2;
-      fz_rope_pair(in[L + d - half], v, cr[d - half], sr[d - half], o1, o2);
-      v = o2;
+      fz_rope_pair(first ? v : other, first ? other : v, cr[pair], sr[pair], o1, o2);
+      v = first ? o1 : o2;
     }
     e[L + d] = Cvt<T>::from_f(v);
   }
@@ -410,7 +424,8 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 rotate_heads_kernel(const T* __restrict__ q, int W, int off, const float* __restrict__ cos_t,
                     const float* __restrict__ sin_t, int rotated, const int* __restrict__ pos,
-                    const int* __restrict__ seq_row, T* __restrict__ out, int Wo, int out_off, int H, int max_len, int* err) {
+                    const int* __restrict__ seq_row, T* __restrict__ out, int Wo, int out_off, int H, int max_len, int* err,
+                    int pairing) {
   fz_grid_launch_dependents();
   fz_grid_wait();
   const int n = blockIdx.x;
@@ -426,14 +441,14 @@ rotate_heads_kernel(const T* __restrict__ q, int W, int off, const float* __rest
     float v = 0.f;
     if (live) {
       v = Cvt<T>::to_f(in[d]);
-      if (d < half) {
+      if (d < rotated) {
+        int partner, pair;
+        bool first;
+        rot_pair_of(d, half, pairing, partner, pair, first);
+        const float other = Cvt<T>::to_f(in[partner]);
         float o1, o2;
-        fz_rope_pair(v, Cvt<T>::to_f(in[d + half]), cr[d], sr[d], o1, o2);
-        v = o1;
-      } else if (d < rotated) {
-        float o1, o2;
-        fz_rope_pair(Cvt<T>::to_f(in[d - half]), v, cr[d - half], sr[d - half], o1, o2);
-        v = o2;
+        fz_rope_pair(first ? v : other, first ? other : v, cr[pair], sr[pair], o1, o2);
+        v = first ? o1 : o2;
       }
     }
     out[((size_t)n * H + hh) * Wo + out_off + d] = Cvt<T>::from_f(v);
@@ -441,9 +456,9 @@ rotate_heads_kernel(const T* __restrict__ q, int W, int off, const float* __rest
 }
 template <typename T>
 void launch_conv_vec(dim3 grid, cudaStream_t stream, const T* h, const T* w, const float* state, const int* seg,
-                     const int* seq_row, T* out, int C, int taps, int residual, int act) {
+                     const int* seq_row, T* out, int C, int taps, int residual, int act, const float* bias) {
   const bool w_ok = ((uintptr_t)w & 15) == 0;       // the grouped weight loads want 16-byte aligned rows of 8 x taps values
-#define FZ_CV(N) fz_launch(short_conv_vec_kernel<T, N>, grid, dim3(128), 0, stream, h, w, state, seg, seq_row, out, C, taps, residual, act)
+#define FZ_CV(N) fz_launch(short_conv_vec_kernel<T, N>, grid, dim3(128), 0, stream, h, w, state, seg, seq_row, out, C, taps, residual, act, bias)
   if (w_ok && taps == 2) FZ_CV(2);
   else if (w_ok && taps == 3) FZ_CV(3);
   else if (w_ok && taps == 4) FZ_CV(4);
@@ -478,20 +493,21 @@ FZ_API int fz_add_rmsnorm_groups(float* x, const float* delta, const void* w, in
 }
 
 FZ_API int fz_short_conv(const void* h, const void* w, float* state, const int* seg, const int* seq_row, void* out,
-                         int dtype, int N, int n_seg, int C, int taps, int residual, int act, cudaStream_t stream) {
+                         int dtype, int N, int n_seg, int C, int taps, int residual, int act, const float* bias,
+                         cudaStream_t stream) {
   if (N <= 0) return FZ_OK;
   if (taps < 1 || taps > MAX_TAPS) return FZ_BAD_SHAPE;
-  const bool vec = C % 8 == 0 && (((uintptr_t)h | (uintptr_t)out | (uintptr_t)state) & 15) == 0;
+  const bool vec = C % 8 == 0 && (((uintptr_t)h | (uintptr_t)out | (uintptr_t)state | (uintptr_t)bias) & 15) == 0;
   const dim3 vgrid(N, (C / 8 + 127) / 128);
   if (dtype == FZ_F32) {
-    if (vec) launch_conv_vec<float>(vgrid, stream, (const float*)h, (const float*)w, (const float*)state, seg, seq_row, (float*)out, C, taps, residual, act);
-    else fz_launch(short_conv_kernel<float>, dim3(N, (C + 255) / 256), dim3(256), 0, stream, (const float*)h, (const float*)w, (const float*)state, seg, seq_row, (float*)out, C, taps, residual, act);
+    if (vec) launch_conv_vec<float>(vgrid, stream, (const float*)h, (const float*)w, (const float*)state, seg, seq_row, (float*)out, C, taps, residual, act, bias);
+    else fz_launch(short_conv_kernel<float>, dim3(N, (C + 255) / 256), dim3(256), 0, stream, (const float*)h, (const float*)w, (const float*)state, seg, seq_row, (float*)out, C, taps, residual, act, bias);
     FZ_LAUNCH_CHECK();
     if (taps > 1 && state != nullptr && n_seg > 0)
       fz_launch(short_conv_state_kernel<float>, dim3(n_seg, (C + 255) / 256), dim3(256), 0, stream, (const float*)h, state, seg, C, taps);
   } else if (dtype == FZ_BF16) {
-    if (vec) launch_conv_vec<__nv_bfloat16>(vgrid, stream, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w, (const float*)state, seg, seq_row, (__nv_bfloat16*)out, C, taps, residual, act);
-    else fz_launch(short_conv_kernel<__nv_bfloat16>, dim3(N, (C + 255) / 256), dim3(256), 0, stream, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w, (const float*)state, seg, seq_row, (__nv_bfloat16*)out, C, taps, residual, act);
+    if (vec) launch_conv_vec<__nv_bfloat16>(vgrid, stream, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w, (const float*)state, seg, seq_row, (__nv_bfloat16*)out, C, taps, residual, act, bias);
+    else fz_launch(short_conv_kernel<__nv_bfloat16>, dim3(N, (C + 255) / 256), dim3(256), 0, stream, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w, (const float*)state, seg, seq_row, (__nv_bfloat16*)out, C, taps, residual, act, bias);
     FZ_LAUNCH_CHECK();
     if (taps > 1 && state != nullptr && n_seg > 0)
       fz_launch(short_conv_state_kernel<__nv_bfloat16>, dim3(n_seg, (C + 255) / 256), dim3(256), 0, stream, (const __nv_bfloat16*)h, state, seg, C, taps);
@@ -530,11 +546,11 @@ FZ_API int fz_select_tokens(const int* tokens, const int* src, const int* prev_i
 FZ_API int fz_latent_cache_write(const float* down, const void* w, int w_dtype, float eps, const float* cos_t,
                                  const float* sin_t, int rotated, const int* pos, const int* seq_row, const int* table,
                                  int mb, void* pool, int dtype, long long page_stride, int page_size, int N, int L, int R,
-                                 int max_len, int num_pages, int* err, cudaStream_t stream) {
+                                 int max_len, int num_pages, int pairing, int* err, cudaStream_t stream) {
   if (N <= 0) return FZ_OK;
-  if (rotated < 0 || rotated > R || rotated % 2) return FZ_BAD_SHAPE;
+  if (rotated < 0 || rotated > R || rotated % 2 || pairing < 0 || pairing > 1) return FZ_BAD_SHAPE;
 #define FZ_LW(TW, T) do { fz_launch(latent_cache_write_kernel<TW, T>, dim3(N), dim3(128), 0, stream, down, (const TW*)w, eps, \
-    cos_t, sin_t, rotated, pos, seq_row, table, mb, (T*)pool, page_stride, page_size, L, R, max_len, num_pages, err); \
+    cos_t, sin_t, rotated, pos, seq_row, table, mb, (T*)pool, page_stride, page_size, L, R, max_len, num_pages, err, pairing); \
     FZ_LAUNCH_CHECK(); return FZ_OK; } while (0)
   if (w_dtype == FZ_F32 && dtype == FZ_F32) FZ_LW(float, float);
   if (w_dtype == FZ_F32 && dtype == FZ_BF16) FZ_LW(float, __nv_bfloat16);
@@ -545,13 +561,13 @@ FZ_API int fz_latent_cache_write(const float* down, const void* w, int w_dtype, 
 
 FZ_API int fz_rotate_heads(const void* q, int W, int off, const float* cos_t, const float* sin_t, int rotated,
                            const int* pos, const int* seq_row, void* out, int Wo, int out_off, int dtype, int N, int H,
-                           int max_len, int* err, cudaStream_t stream) {
+                           int max_len, int pairing, int* err, cudaStream_t stream) {
   if (N <= 0) return FZ_OK;
-  if (rotated < 0 || rotated > W - off || rotated % 2) return FZ_BAD_SHAPE;
+  if (rotated < 0 || rotated > W - off || rotated % 2 || pairing < 0 || pairing > 1) return FZ_BAD_SHAPE;
   if (dtype == FZ_F32)
-    fz_launch(rotate_heads_kernel<float>, dim3(N), dim3(256), 0, stream, (const float*)q, W, off, cos_t, sin_t, rotated, pos, seq_row, (float*)out, Wo, out_off, H, max_len, err);
+    fz_launch(rotate_heads_kernel<float>, dim3(N), dim3(256), 0, stream, (const float*)q, W, off, cos_t, sin_t, rotated, pos, seq_row, (float*)out, Wo, out_off, H, max_len, err, pairing);
   else if (dtype == FZ_BF16)
-    fz_launch(rotate_heads_kernel<__nv_bfloat16>, dim3(N), dim3(256), 0, stream, (const __nv_bfloat16*)q, W, off, cos_t, sin_t, rotated, pos, seq_row, (__nv_bfloat16*)out, Wo, out_off, H, max_len, err);
+    fz_launch(rotate_heads_kernel<__nv_bfloat16>, dim3(N), dim3(256), 0, stream, (const __nv_bfloat16*)q, W, off, cos_t, sin_t, rotated, pos, seq_row, (__nv_bfloat16*)out, Wo, out_off, H, max_len, err, pairing);
   else
     return FZ_BAD_DTYPE;
   FZ_LAUNCH_CHECK();

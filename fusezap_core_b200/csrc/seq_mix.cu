@@ -132,13 +132,22 @@ struct AttnArgs {
   int unit_chunks, max_units; float* part;         // unit kernel: chunks per run, runs per row, (m, l, acc[dv]) per (row, head, run)
   float softcap;                                   // > 0: the scaled score s becomes softcap * tanh(s / softcap)
   const float* gate; int gate_ld, gate_off;        // not null: head h's result is multiplied by sigmoid(gate[n gate_ld + gate_off + h])
+  int span;                                        // > 0: a row sees only the keys of its own block of `span` positions
 };
+
+// The first key a row at position p sees (kept first tokens aside): the window's start, and with a chunked mask not
+// before the start of the row's own block of `span` positions. It never falls as p grows.
+__device__ __forceinline__ int first_seen(int p, int window, int span) {
+  int lo = window > 0 ? max(0, p - window + 1) : 0;
+  if (span > 0) lo = max(lo, p - p % span);
+  return lo;
+}
 
 // The chunks a row at position p walks: `first_end + 1` chunks of kept tokens, then chunks c2 .. p / CHUNK.
 struct ChunkWalk {
   int lo, kept, first_end, c2, count;
-  __device__ ChunkWalk(int p_first, int p_last, int window, int keep_first) {
-    lo = window > 0 ? max(0, p_first - window + 1) : 0;
+  __device__ ChunkWalk(int p_first, int p_last, int window, int keep_first, int span) {
+    lo = first_seen(p_first, window, span);
     kept = min(keep_first, lo);                    // keys 0 .. kept-1 are seen although they lie before the window
     first_end = kept > 0 ? (kept - 1) / CHUNK : -1;
     c2 = max(lo / CHUNK, first_end + 1);
@@ -334,7 +343,7 @@ sink_attention_tile_kernel(const AttnArgs a) {
     for (int i = 0; i < DPL; ++i) acc[x][i] = 0.f;
   }
   const int p_first = pos0 + r0, p_last = p_first + nr - 1;
-  const ChunkWalk walk(p_first, p_last, a.window, a.keep_first);
+  const ChunkWalk walk(p_first, p_last, a.window, a.keep_first, a.span);
   const int* trow = a.table + (size_t)a.seq_row[row0] * a.mb;
   const int pairs = nr * G;
   for (int it = 0; it < walk.count; ++it) {
@@ -347,7 +356,7 @@ sink_attention_tile_kernel(const AttnArgs a) {
       const int pr = warp + x * ATT_WARPS;
       if (pr >= pairs) break;
       const int p = p_first + pr / G;
-      const int lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
+      const int lo = first_seen(p, a.window, a.span);
       pair_chunk<DPL>(Qs + pr * dk, Ks, Vs, c, p, lo, a.keep_first, a.scale, a.softcap, dk, dv, m[x], l[x], acc[x]);
     }
   }
@@ -370,7 +379,7 @@ sink_attention_unit_kernel(const AttnArgs a) {
   const int row = a.seq_row[n], p = a.pos[n];
   fz_grid_wait();
   if (row < 0) return;
-  const ChunkWalk walk(p, p, a.window, a.keep_first);
+  const ChunkWalk walk(p, p, a.window, a.keep_first, a.span);
   const int it0 = blockIdx.z * a.unit_chunks;
   if (it0 >= walk.count) return;
   extern __shared__ __align__(16) float smem[];
@@ -437,7 +446,7 @@ sink_attention_merge_kernel(const AttnArgs a) {
     for (int d = threadIdx.x; d < dv; d += blockDim.x) o[d] = Cvt<T>::from_f(0.f);
     return;
   }
-  const ChunkWalk walk(p, p, a.window, a.keep_first);
+  const ChunkWalk walk(p, p, a.window, a.keep_first, a.span);
   const int runs = (walk.count + a.unit_chunks - 1) / a.unit_chunks;
   // the largest of the runs' maxima first, then every run's term with its own factor: no load waits for a sum, and the
   // order of the sums is that of the runs, whatever else the step holds
@@ -1084,25 +1093,114 @@ router_topk_kernel(const float* __restrict__ logits, int ld, int N, int E, int t
   }
 }
 
-// out[n] = sum_k w[n, k] terms[n top + k] (+ sigmoid(gl[n, col]) shared[n]); rows of padding give zeros.
+// out[n] = scale * (add[n] + sum_k w[n, k] terms[n top + k] (+ sigmoid(gl[n, col]) shared[n])); a null gl counts as a gate
+// of 1, a null add as zero, and the product with scale is left out when it is 1; rows of padding give zeros.
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* __restrict__ terms, const float* __restrict__ w, int top, const float* __restrict__ shared,
                    const float* __restrict__ gl, int ldg, int col, const int* __restrict__ seq_row, float* __restrict__ out,
-                   int N, int D) {
+                   int N, int D, const float* __restrict__ add, float scale) {
   fz_grid_launch_dependents();
   fz_grid_wait();
   const int n = blockIdx.x;
   const bool pad = seq_row[n] < 0;
-  float sg = 0.f;
-  if (!pad && shared != nullptr) sg = 1.0f / (1.0f + expf(-gl[(size_t)n * ldg + col]));
+  float sg = 1.f;
+  if (!pad && shared != nullptr && gl != nullptr) sg = 1.0f / (1.0f + expf(-gl[(size_t)n * ldg + col]));
   for (int d = blockIdx.y * blockDim.x + threadIdx.x; d < D; d += gridDim.y * blockDim.x) {
     float acc = 0.f;
     if (!pad) {
       for (int k = 0; k < top; ++k) acc = __fmaf_rn(w[(size_t)n * top + k], terms[((size_t)n * top + k) * D + d], acc);
       if (shared != nullptr) acc = __fmaf_rn(sg, shared[(size_t)n * D + d], acc);
+      if (add != nullptr) acc = __fadd_rn(acc, add[(size_t)n * D + d]);
+      if (scale != 1.f) acc = __fmul_rn(acc, scale);
     }
     out[(size_t)n * D + d] = acc;
   }
+}
+
+// ------------------------------------------------------------------------------ real-gated linear recurrent unit
+// Per channel c of part b (W / B channels each): r = sigmoid(g_r + bias), i = sigmoid(g_i + bias),
+// a = exp(-k_c r) with k_c = sharpness * softplus(lam_c), S <- a S + sqrt(1 - a^2) (i u), out = S y. Everything in
+// float32 with explicit roundings, so that the two forms below give the same bits: 1 - a^2 is taken as -expm1(-2 k_c r),
+// which keeps its digits where a is close to one.
+//
+// Long portions run in two launches: `rglru_cook_kernel` (every (row, channel) on its own) overwrites the two gate
+// inputs by a and b = sqrt(1 - a^2) i u, and the scan, a thread per (portion, channel), walks the portion's tokens with
+// one fused multiply-add each, sixteen tokens' loads in flight. Steps of short portions (decoded tokens) run the scan
+// alone, which then cooks a and b itself.
+__device__ __forceinline__ float rglru_softplus(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
+__device__ __forceinline__ void rglru_cook(float gr, float gi, float br, float bi, float k, float u, float& a, float& b) {
+  const float r = 1.0f / (1.0f + expf(-__fadd_rn(gr, br)));
+  const float i = 1.0f / (1.0f + expf(-__fadd_rn(gi, bi)));
+  const float la = -__fmul_rn(k, r);
+  a = expf(la);
+  b = __fmul_rn(sqrtf(-expm1f(__fmul_rn(2.f, la))), __fmul_rn(i, u));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+rglru_cook_kernel(const T* __restrict__ u, float* __restrict__ gates, const float* __restrict__ gbias,
+                  const float* __restrict__ lam, float sharp, const int* __restrict__ seq_row, int W, int bw, long long total) {
+  fz_grid_launch_dependents();
+  fz_grid_wait();
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+    const long long n = idx / W;
+    const int c = (int)(idx - n * W);
+    if (seq_row[n] < 0) continue;
+    const int part = c / bw, gcol = part * 2 * bw + (c - part * bw);
+    float* g = gates + n * 2 * W + gcol;
+    float a, b;
+    rglru_cook(g[0], g[bw], gbias[gcol], gbias[gcol + bw], __fmul_rn(sharp, rglru_softplus(lam[c])), Cvt<T>::to_f(u[idx]), a, b);
+    g[0] = a;
+    g[bw] = b;
+  }
+}
+
+constexpr int RGLRU_AHEAD = 16;
+template <typename T, bool COOKED>
+__global__ void __launch_bounds__(64)
+rglru_scan_kernel(const T* __restrict__ u, const float* __restrict__ gates, const float* __restrict__ gbias,
+                  const float* __restrict__ lam, const T* __restrict__ y, float sharp, float* __restrict__ state,
+                  const int* __restrict__ seg, T* __restrict__ out, int W, int bw) {
+  fz_grid_launch_dependents();
+  const int s = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  const int row0 = seg[4 * s], cnt = seg[4 * s + 1], slot = seg[4 * s + 3];
+  int gcol = 0;
+  float k = 0.f, br = 0.f, bi = 0.f;
+  if (c < W) {
+    const int part = c / bw;
+    gcol = part * 2 * bw + (c - part * bw);
+    if (!COOKED) {
+      k = __fmul_rn(sharp, rglru_softplus(lam[c]));
+      br = gbias[gcol];
+      bi = gbias[gcol + bw];
+    }
+  }
+  fz_grid_wait();
+  if (c >= W || cnt <= 0 || slot < 0) return;
+  float S = state[(size_t)slot * W + c];
+  for (int t0 = 0; t0 < cnt; t0 += RGLRU_AHEAD) {
+    float a[RGLRU_AHEAD], b[RGLRU_AHEAD], yy[RGLRU_AHEAD];
+#pragma unroll
+    for (int i = 0; i < RGLRU_AHEAD; ++i) {
+      a[i] = 1.f; b[i] = 0.f; yy[i] = 0.f;
+      if (t0 + i < cnt) {
+        const size_t n = (size_t)(row0 + t0 + i);
+        const float* g = gates + n * 2 * W + gcol;
+        yy[i] = Cvt<T>::to_f(y[n * W + c]);
+        if (COOKED) { a[i] = g[0]; b[i] = g[bw]; }
+        else rglru_cook(g[0], g[bw], br, bi, k, Cvt<T>::to_f(u[n * W + c]), a[i], b[i]);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < RGLRU_AHEAD; ++i) {
+      if (t0 + i < cnt) {
+        S = __fmaf_rn(a[i], S, b[i]);
+        out[(size_t)(row0 + t0 + i) * W + c] = Cvt<T>::from_f(__fmul_rn(S, yy[i]));
+      }
+    }
+  }
+  state[(size_t)slot * W + c] = S;
 }
 
 struct Terms {
@@ -1215,8 +1313,9 @@ FZ_API int fz_sink_attention_check(int Hq, int Hkv, int dk, int dv) {
 }
 
 // How many runs of `unit_chunks` chunks a row can have at most, for contexts up to max_context.
-FZ_API int fz_sink_attention_units(int window, int keep_first, int max_context, int unit_chunks) {
-  const int keys = window > 0 ? (window < max_context ? window : max_context) : max_context;
+FZ_API int fz_sink_attention_units(int window, int keep_first, int max_context, int unit_chunks, int span) {
+  int keys = window > 0 ? (window < max_context ? window : max_context) : max_context;
+  if (span > 0 && span < keys) keys = span;
   const int kept = window > 0 ? (keep_first < max_context ? keep_first : max_context) : 0;
   const int chunks = (keys + CHUNK - 1) / CHUNK + 1 + (kept + CHUNK - 1) / CHUNK;
   return (chunks + unit_chunks - 1) / unit_chunks;
@@ -1229,13 +1328,14 @@ FZ_API int fz_sink_attention(const void* q, const void* k_pool, const void* v_po
                              long long head_stride, long long tok_stride, int page_size, int n_pages, void* out, int dtype,
                              int N, int Hq, int Hkv, int dk, int dv, float scale, int window, int keep_first,
                              const float* sink, int unit_chunks, int units, float* part, float softcap, const float* gate,
-                             int gate_ld, int gate_off, int* err, cudaStream_t stream) {
+                             int gate_ld, int gate_off, int span, int* err, cudaStream_t stream) {
   if (N <= 0 || n_seg <= 0) return FZ_OK;
+  if (span < 0 || (span > 0 && keep_first > 0)) return FZ_BAD_SHAPE;
   if (softcap < 0.f || (gate != nullptr && (gate_off < 0 || gate_off + Hq > gate_ld))) return FZ_BAD_SHAPE;
   if (fz_sink_attention_check(Hq, Hkv, dk, dv) != FZ_OK || page_size <= 0 || window < 0 || keep_first < 0 || max_portion <= 0 ||
       (units > 0 && (unit_chunks <= 0 || part == nullptr || units > 65535))) return FZ_BAD_SHAPE;
   AttnArgs a = {q, k_pool, v_pool, pos, seq_row, seg, table, mb, page_stride, head_stride, tok_stride, page_size, n_pages, out,
-                Hq, Hkv, dk, dv, scale, window, keep_first, sink, err, N, 1, unit_chunks, units, part, softcap, gate, gate_ld, gate_off};
+                Hq, Hkv, dk, dv, scale, window, keep_first, sink, err, N, 1, unit_chunks, units, part, softcap, gate, gate_ld, gate_off, span};
   if (dtype == FZ_F32) return dispatch_sink<float>(a, N, n_seg, max_portion, units, stream);
   if (dtype == FZ_BF16) return dispatch_sink<__nv_bfloat16>(a, N, n_seg, max_portion, units, stream);
   return FZ_BAD_DTYPE;
@@ -1389,10 +1489,43 @@ FZ_API int fz_router_topk(const float* logits, int ld, int N, int E, int top, in
 }
 
 FZ_API int fz_moe_combine(const float* terms, const float* w, int top, const float* shared, const float* gl, int ldg, int col,
-                          const int* seq_row, float* out, int N, int D, cudaStream_t stream) {
+                          const int* seq_row, float* out, int N, int D, const float* add, float scale, cudaStream_t stream) {
   if (N <= 0 || D <= 0) return FZ_OK;
   const int by = (D + 1023) / 1024 > 0 ? (D + 1023) / 1024 : 1;
-  fz_launch(moe_combine_kernel, dim3(N, by), dim3(256), 0, stream, terms, w, top, shared, gl, ldg, col, seq_row, out, N, D);
+  fz_launch(moe_combine_kernel, dim3(N, by), dim3(256), 0, stream, terms, w, top, shared, gl, ldg, col, seq_row, out, N, D, add,
+            scale);
+  FZ_LAUNCH_CHECK();
+  return FZ_OK;
+}
+
+// cooked != 0: two launches (the gate inputs are overwritten by the recurrence's coefficients); else the scan alone.
+FZ_API int fz_rglru_scan(const void* u, float* gates, const float* gbias, const float* lam, const void* y, float sharp,
+                         float* state, const int* seg, int n_seg, const int* seq_row, void* out, int dtype, int N, int W, int B,
+                         int cooked, cudaStream_t stream) {
+  if (N <= 0 || n_seg <= 0) return FZ_OK;
+  if (W <= 0 || B <= 0 || W % B || n_seg > 65535 * 32) return FZ_BAD_SHAPE;
+  if (dtype != FZ_F32 && dtype != FZ_BF16) return FZ_BAD_DTYPE;
+  const int bw = W / B;
+  const dim3 grid(n_seg, (W + 63) / 64);
+  if (cooked) {
+    const long long total = (long long)N * W;
+    long long blocks = (total + 255) / 256;
+    if (blocks > 148LL * 16) blocks = 148LL * 16;
+    if (dtype == FZ_F32)
+      fz_launch(rglru_cook_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, (const float*)u, gates, gbias, lam, sharp, seq_row, W, bw, total);
+    else
+      fz_launch(rglru_cook_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(256), 0, stream, (const __nv_bfloat16*)u, gates, gbias, lam, sharp, seq_row, W, bw, total);
+    FZ_LAUNCH_CHECK();
+    if (dtype == FZ_F32)
+      fz_launch(rglru_scan_kernel<float, true>, grid, dim3(64), 0, stream, (const float*)u, gates, gbias, lam, (const float*)y, sharp, state, seg, (float*)out, W, bw);
+    else
+      fz_launch(rglru_scan_kernel<__nv_bfloat16, true>, grid, dim3(64), 0, stream, (const __nv_bfloat16*)u, gates, gbias, lam, (const __nv_bfloat16*)y, sharp, state, seg, (__nv_bfloat16*)out, W, bw);
+  } else {
+    if (dtype == FZ_F32)
+      fz_launch(rglru_scan_kernel<float, false>, grid, dim3(64), 0, stream, (const float*)u, gates, gbias, lam, (const float*)y, sharp, state, seg, (float*)out, W, bw);
+    else
+      fz_launch(rglru_scan_kernel<__nv_bfloat16, false>, grid, dim3(64), 0, stream, (const __nv_bfloat16*)u, gates, gbias, lam, (const __nv_bfloat16*)y, sharp, state, seg, (__nv_bfloat16*)out, W, bw);
+  }
   FZ_LAUNCH_CHECK();
   return FZ_OK;
 }

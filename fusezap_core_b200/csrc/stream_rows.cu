@@ -159,8 +159,44 @@ activate_kernel(const float* __restrict__ src, int ld, int off, int kind, T* __r
     if (kind == 0) v = tanhf(z);
     else if (kind == 1) v = 1.0f / (1.0f + expf(-z));
     else if (kind == 2) v = z / (1.0f + expf(-z));
-    else v = 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    else if (kind == 3) v = 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    else v = z;
     out[idx] = Cvt<T>::from_f(v);
+  }
+}
+
+// out = T(x * act(gate[:, off + j])): the activation (kinds of `activate_kernel`) and the product in float32. out may be x.
+template <typename T>
+__global__ void __launch_bounds__(256)
+gate_multiply_kernel(const T* x, const float* __restrict__ gate, int ld, int off, int kind, T* out, int W, long long total) {
+  fz_grid_launch_dependents();
+  fz_grid_wait();
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+    const long long n = idx / W;
+    const int j = (int)(idx - n * W);
+    const float z = gate[n * ld + off + j];
+    float v;
+    if (kind == 0) v = tanhf(z);
+    else if (kind == 1) v = 1.0f / (1.0f + expf(-z));
+    else if (kind == 2) v = z / (1.0f + expf(-z));
+    else if (kind == 3) v = 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    else v = z;
+    out[idx] = Cvt<T>::from_f(__fmul_rn(Cvt<T>::to_f(x[idx]), v));
+  }
+}
+
+// dst[:, doff + j] = (1 - w) dst[:, doff + j] + w src[:, soff + j], w = weight[0]: two rounded products, then their sum.
+__global__ void __launch_bounds__(256)
+blend_columns_kernel(float* __restrict__ dst, int ldd, int doff, const float* __restrict__ src, int lds, int soff,
+                     const float* __restrict__ weight, int W, long long total) {
+  fz_grid_launch_dependents();
+  const float w = weight[0], keep = __fsub_rn(1.0f, w);
+  fz_grid_wait();
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+    const long long n = idx / W;
+    const int j = (int)(idx - n * W);
+    float* d = dst + n * ldd + doff + j;
+    *d = __fadd_rn(__fmul_rn(keep, *d), __fmul_rn(w, src[n * lds + soff + j]));
   }
 }
 }  // namespace
@@ -224,13 +260,42 @@ FZ_API int fz_depth_average_norm(float* streams, int L1, int depth, const float*
 FZ_API int fz_activate(const float* src, int ld, int off, int kind, void* out, int dtype, int N, int W, cudaStream_t stream) {
   const long long total = (long long)N * W;
   if (total <= 0) return FZ_OK;
-  if (kind < 0 || kind > 3 || off < 0 || off + W > ld) return FZ_BAD_SHAPE;
+  if (kind < 0 || kind > 4 || off < 0 || off + W > ld) return FZ_BAD_SHAPE;
   long long blocks = (total + 255) / 256;
   if (blocks > 148LL * 16) blocks = 148LL * 16;
   if (dtype == FZ_F32) fz_launch(activate_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, src, ld, off, kind, (float*)out, W, total);
   else if (dtype == FZ_BF16)
     fz_launch(activate_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(256), 0, stream, src, ld, off, kind, (__nv_bfloat16*)out, W, total);
   else return FZ_BAD_DTYPE;
+  FZ_LAUNCH_CHECK();
+  return FZ_OK;
+}
+
+FZ_API int fz_gate_multiply(const void* x, const float* gate, int ld, int off, int kind, void* out, int dtype, int N, int W,
+                            cudaStream_t stream) {
+  const long long total = (long long)N * W;
+  if (total <= 0) return FZ_OK;
+  if (kind < 0 || kind > 4 || off < 0 || off + W > ld) return FZ_BAD_SHAPE;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148LL * 16) blocks = 148LL * 16;
+  if (dtype == FZ_F32)
+    fz_launch(gate_multiply_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, (const float*)x, gate, ld, off, kind, (float*)out, W, total);
+  else if (dtype == FZ_BF16)
+    fz_launch(gate_multiply_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(256), 0, stream, (const __nv_bfloat16*)x, gate, ld, off,
+              kind, (__nv_bfloat16*)out, W, total);
+  else return FZ_BAD_DTYPE;
+  FZ_LAUNCH_CHECK();
+  return FZ_OK;
+}
+
+FZ_API int fz_blend_columns(float* dst, int ldd, int doff, const float* src, int lds, int soff, const float* weight, int N, int W,
+                            cudaStream_t stream) {
+  const long long total = (long long)N * W;
+  if (total <= 0) return FZ_OK;
+  if (doff < 0 || doff + W > ldd || soff < 0 || soff + W > lds || weight == nullptr) return FZ_BAD_SHAPE;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148LL * 16) blocks = 148LL * 16;
+  fz_launch(blend_columns_kernel, dim3((int)blocks), dim3(256), 0, stream, dst, ldd, doff, src, lds, soff, weight, W, total);
   FZ_LAUNCH_CHECK();
   return FZ_OK;
 }

@@ -208,6 +208,8 @@ class StepContext:
     model: DecoderModel
     token_ids: torch.Tensor | None = None     # the step's token ids on the device, int32 (N,), for parts that declare
                                               # the step need "token_ids"; set before the first layer runs
+    shared: dict = field(default_factory=dict)    # what a layer leaves for later layers of the same step (views of
+                                                  # scratch buffers under a key that both name); emptied at each step
 
 
 class StepRunner:
@@ -254,6 +256,7 @@ class StepRunner:
                 end()
 
     def _forward(self, model, ctx, meta, spec, ids_out):
+        ctx.shared.clear()
         x = self.ws.get("x", (meta.n_rows, spec.hidden_size), torch.float32)
         src = meta.src if self.prev_ids is not None else None
         if model.embed_scale != 1.0:

@@ -55,14 +55,15 @@ class Ops:
         raise NotImplementedError
 
     def short_conv(self, h: torch.Tensor, w: torch.Tensor, state: torch.Tensor | None, meta: Any, out: torch.Tensor,
-                   residual: bool = True, activation: str | None = None) -> None:
+                   residual: bool = True, activation: str | None = None, bias: torch.Tensor | None = None) -> None:
         """Causal convolution over time within each portion of the step (meta.seg: first row, rows, first position,
         state slot). h, out: (N, C) T; w: (C, taps) T; state: (slots, taps - 1, C) float32, the last taps - 1 inputs of
         each request so far, oldest first. For the row at place i of its portion:
         out = (h if residual) + sum_j w[:, j] * in(i - taps + 1 + j), in(k) = h[first row + k] for k >= 0, else
         state[slot, taps - 1 + k]. The sum is float32, j rising, rounded once. Afterwards state[slot] holds the portion's
         request's last taps - 1 inputs. Padding rows give zeros. activation "silu": out = z * sigmoid(z) of
-        the float32 sum z (residual included), rounded once."""
+        the float32 sum z (residual included), rounded once. bias (C,) float32: added to the sum after the taps, before
+        the residual and the activation."""
         raise NotImplementedError
 
     def gated_sum(self, a: torch.Tensor, gate_a: torch.Tensor | None, f: torch.Tensor | None, gate_f: torch.Tensor | None,
@@ -81,15 +82,16 @@ class Ops:
         raise NotImplementedError
 
     def latent_cache_write(self, down: torch.Tensor, norm_weight: torch.Tensor, eps: float, cos: torch.Tensor,
-                           sin: torch.Tensor, rotated: int, meta: Any, cache: Any) -> None:
+                           sin: torch.Tensor, rotated: int, meta: Any, cache: Any, pairing: int = 0) -> None:
         """down: (N, L + R) float32, cache.keys: (pages, page_size, L + R) T. For every live row: the first L values
         are divided by their root mean square (eps inside the root) and multiplied by norm_weight (L,); of the last R,
         the first `rotated` are turned by the row's position (pairs i, i + rotated/2, tables (max_len, rotated/2)), the
-        rest pass; the L + R values are rounded once and stored at the row's place in its request's pages."""
+        rest pass; the L + R values are rounded once and stored at the row's place in its request's pages. pairing 1:
+        pairs 2i, 2i + 1 instead."""
         raise NotImplementedError
 
     def rotate_heads(self, q: torch.Tensor, offset: int, cos: torch.Tensor, sin: torch.Tensor, rotated: int, meta: Any,
-                     out: torch.Tensor, out_offset: int) -> None:
+                     out: torch.Tensor, out_offset: int, pairing: int = 0) -> None:
         """q: (N, H, W) T, out: (N, H, Wo) T. out[n, h, out_offset : out_offset + W - offset] = q[n, h, offset:] with its
         first `rotated` values turned by the row's position (as in `latent_cache_write`); float32 arithmetic."""
         raise NotImplementedError
@@ -97,14 +99,15 @@ class Ops:
     def linear_heads(self, a: torch.Tensor, a_offset: int, k: int, w: torch.Tensor, out: torch.Tensor,
                      out_offset: int) -> None:
         """One product per head: out[n, h, out_offset : out_offset + M] = w[h] . a[n, h, a_offset : a_offset + k];
-        a: (N, H, Wa) T, w: (H, M, k) T, out: (N, H, Wo) T; float32 accumulation over k in rising order."""
+        a: (N, H, Wa) T, w: (H, M, k) T, out: (N, H, Wo) T or float32; float32 accumulation over k in rising order."""
         raise NotImplementedError
 
     def latent_attention(self, q: torch.Tensor, cache: Any, meta: Any, out: torch.Tensor, value_width: int, scale: float,
-                         window: int) -> None:
+                         window: int, sink: torch.Tensor | None = None) -> None:
         """q: (N, H, W) T; cache.keys: (pages, page_size, W) T, one vector e_j per cached token, shared by all heads.
         out[n, h] = sum_j softmax_j((q[n, h] . e_j) * scale) e_j[:value_width] over the keys j of the row's own request
-        with max(0, p - window + 1) <= j <= p (window 0: 0 <= j <= p), p = meta.pos[n]; out: (N, H, value_width) T."""
+        with max(0, p - window + 1) <= j <= p (window 0: 0 <= j <= p), p = meta.pos[n]; out: (N, H, value_width) T.
+        sink (H,) float32: the softmax's denominator of head h also holds exp(sink[h]) (not scaled, no value)."""
         raise NotImplementedError
 
     def route_by_table(self, token_ids: torch.Tensor, meta: Any, table: torch.Tensor, num_experts: int, align: int = 1) -> Any:
@@ -174,7 +177,29 @@ class Ops:
 
     def activate(self, src: torch.Tensor, offset: int, kind: str, out: torch.Tensor) -> None:
         """out[n, j] = T(act(src[n, offset + j])) for the columns of out; src float32 (N, any width); kind "tanh",
-        "sigmoid", "silu", "gelu_tanh", computed in float32 and rounded once. Padding rows need not be zero."""
+        "sigmoid", "silu", "gelu_tanh", "identity", computed in float32 and rounded once. Padding rows need not be zero."""
+        raise NotImplementedError
+
+    def gate_multiply(self, x: torch.Tensor, gate: torch.Tensor, gate_offset: int, kind: str, out: torch.Tensor) -> None:
+        """out[n, j] = T(x[n, j] * act(gate[n, gate_offset + j])); x, out (N, W) T (out may be x), gate float32 (N, any
+        width), act as in `activate`; the activation and the product in float32, rounded once."""
+        raise NotImplementedError
+
+    def blend_columns(self, dst: torch.Tensor, dst_offset: int, src: torch.Tensor, src_offset: int, width: int,
+                      weight: torch.Tensor) -> None:
+        """dst[n, dst_offset + j] = (1 - w) * dst[n, dst_offset + j] + w * src[n, src_offset + j] for j < width, in place;
+        dst, src float32 (N, any width), w = weight[0] (float32, on the device). float32: the two products rounded, then
+        their sum."""
+        raise NotImplementedError
+
+    def rglru_scan(self, u: torch.Tensor, gates: torch.Tensor, gate_bias: torch.Tensor, lam: torch.Tensor, y: torch.Tensor,
+                   sharpness: float, state: torch.Tensor, meta: Any, out: torch.Tensor) -> None:
+        """u, y, out: (N, W) T; gates: (N, B, 2 W/B) float32, part b = [recurrence gate | input gate] before bias and
+        sigmoid; gate_bias (B, 2 W/B), lam (W,) float32; state (slots, W) float32. Per portion (meta.seg), token by token,
+        per channel c of part b: r = sigmoid(gates[n, b, j] + bias), i = sigmoid(gates[n, b, W/B + j] + bias), a =
+        exp(-sharpness * r * softplus(lam[c])), S = a * S + sqrt(1 - a^2) * (i * u[n, c]) from the slot's state,
+        out[n, c] = T(S * y[n, c]). float32 throughout; the slot's state is that after the portion's last token.
+        Padding rows give zeros. softplus(z) = max(z, 0) + log1p(exp(-|z|))."""
         raise NotImplementedError
 
     def hashed_pair_embed(self, table: torch.Tensor, token_ids: torch.Tensor, meta: Any, state: torch.Tensor,
@@ -220,12 +245,13 @@ class Ops:
 
     def sink_attention(self, q: torch.Tensor, cache: Any, meta: Any, out: torch.Tensor, num_heads: int, num_kv_heads: int,
                        key_dim: int, value_dim: int, scale: float, window: int, keep_first: int,
-                       sink: torch.Tensor | None, softcap: float = 0.0, gate: tuple | None = None) -> None:
+                       sink: torch.Tensor | None, softcap: float = 0.0, gate: tuple | None = None, span: int = 0) -> None:
         """out[n, h] = sum_j e_j v_j / (sum_j e_j + exp(sink[h] - m)), e_j = exp(s_j - m), s_j = (q[n, h] . k_j) * scale,
         over the keys j <= p of the row's own request with p - j < window or j < keep_first (window 0: all), p =
         meta.pos[n], m the largest of the scores and sink[h]; sink None: no such term. kv head h // (Hq / Hkv).
         out: (N, Hq dv) T. softcap c > 0: s_j = c * tanh((q . k_j) * scale / c). gate (g, offset), g float32 (N, any
-        width): out[n, h] is multiplied by sigmoid(g[n, offset + h]) before it is rounded."""
+        width): out[n, h] is multiplied by sigmoid(g[n, offset + h]) before it is rounded. span s > 0: key j is seen
+        only if also floor(j / s) = floor(p / s) (keep_first must then be 0)."""
         raise NotImplementedError
 
     def weighted_sum(self, terms: list, weights: list, out: torch.Tensor) -> None:
@@ -242,10 +268,12 @@ class Ops:
         raise NotImplementedError
 
     def moe_combine(self, terms: torch.Tensor, weights: torch.Tensor, shared: torch.Tensor | None,
-                    gate_logits: torch.Tensor | None, gate_column: int, out: torch.Tensor) -> None:
+                    gate_logits: torch.Tensor | None, gate_column: int, out: torch.Tensor,
+                    add: torch.Tensor | None = None, scale: float = 1.0) -> None:
         """out[n] = sum_k weights[n, k] * terms[n * top + k] (+ sigmoid(gate_logits[n, gate_column]) * shared[n]); all
-        float32; terms (N top, D), weights (N, top), shared (N, D), the sum in rising k and the shared term last.
-        Padding rows give zeros."""
+        float32; terms (N top, D), weights (N, top), shared (N, D), the sum in rising k and the shared term last
+        (gate_logits None: the shared term is added as it is). add (N, D) float32 and scale: out = scale * (add + the
+        sum). Padding rows give zeros."""
         raise NotImplementedError
 
     def linear(self, a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor) -> None:

@@ -24,6 +24,8 @@ _DEVICE_ERRORS = {1: "a token id lies outside the embedding table", 2: "a positi
                   16: "a selected row lies outside the step"}
 
 
+_ACTIVATIONS = {"tanh": 0, "sigmoid": 1, "silu": 2, "gelu_tanh": 3, "identity": 4}
+RGLRU_COOK_ROWS = 4  # recurrent unit: steps whose longest portion is longer compute the recurrence's coefficients in a launch of their own
 SINK_MMA_ROWS = 16  # windowed attention with a sink: steps whose longest portion has this many rows go to the tensor-core kernel
 LONG_PORTION = 8    # attention: portions of at least this many tokens go to the tile (prefill) kernels
 TILE_ROWS = 128     # token rows per tile of those kernels
@@ -631,7 +633,7 @@ class CudaOps(Ops):
             raise KernelError("select_tokens: row counts differ")
         self._check(self.mix.fz_select_tokens(_p(tokens), _p(src), _p(prev_ids), _p(out), c_int(n), self._stream()), "select_tokens")
 
-    def short_conv(self, h, w, state, meta, out, residual: bool = True, activation: str | None = None) -> None:
+    def short_conv(self, h, w, state, meta, out, residual: bool = True, activation: str | None = None, bias=None) -> None:
         if activation not in (None, "silu"):
             raise KernelError(f"short_conv: activation {activation!r} is not one of None, 'silu'")
         self._want(h, "convolution input", (self.dtype,), 2)
@@ -639,6 +641,10 @@ class CudaOps(Ops):
         self._want(out, "convolution output", (self.dtype,), 2)
         n, c = h.shape
         taps = w.shape[1]
+        if bias is not None:
+            self._want(bias, "convolution bias", (torch.float32,), 1)
+            if bias.shape[0] != c:
+                raise KernelError(f"short_conv: bias {tuple(bias.shape)} for {c} channels")
         if w.shape[0] != c or out.shape != h.shape:
             raise KernelError(f"short_conv: h {tuple(h.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
         if taps > 1:
@@ -649,7 +655,7 @@ class CudaOps(Ops):
                 raise KernelError(f"short_conv: state {tuple(state.shape)}, expected (slots, {taps - 1}, {c})")
         self._check(self.mix.fz_short_conv(_p(h), _p(w), _p(state), _p(meta.seg), _p(meta.seq_row), _p(out),
                                            c_int(_CODE[self.dtype]), c_int(n), c_int(getattr(meta, "max_segments", meta.n_segments)), c_int(c), c_int(taps),
-                                           c_int(1 if residual else 0), c_int(1 if activation else 0), self._stream()), "short_conv",
+                                           c_int(1 if residual else 0), c_int(1 if activation else 0), _p(bias), self._stream()), "short_conv",
                     n * c * 2 * h.element_size())
         if taps > 1:
             self.launches += 1    # the state update
@@ -687,7 +693,7 @@ class CudaOps(Ops):
                               f"(pages, {cache.page_size}, {width}) with contiguous pages")
         return pool, pool.stride(0)
 
-    def latent_cache_write(self, down, norm_weight, eps, cos, sin, rotated, meta, cache) -> None:
+    def latent_cache_write(self, down, norm_weight, eps, cos, sin, rotated, meta, cache, pairing: int = 0) -> None:
         self._want(down, "latent projection", (torch.float32,), 2)
         self._want(norm_weight, "latent norm weight", (torch.float32, torch.bfloat16), 1)
         self._want(cos, "cos table", (torch.float32,), 2)
@@ -703,9 +709,10 @@ class CudaOps(Ops):
             _p(down), _p(norm_weight), c_int(_CODE[norm_weight.dtype]), c_float(eps), _p(cos), _p(sin), c_int(rotated),
             _p(meta.pos), _p(meta.seq_row), _p(table), c_int(table.shape[1]), _p(pool), c_int(_CODE[self.dtype]),
             c_longlong(page_stride), c_int(cache.page_size), c_int(n), c_int(lat), c_int(rot), c_int(cos.shape[0]),
-            c_int(pool.shape[0]), _p(self.err), self._stream()), "latent_cache_write", n * width * (4 + pool.element_size()))
+            c_int(pool.shape[0]), c_int(pairing), _p(self.err), self._stream()), "latent_cache_write",
+            n * width * (4 + pool.element_size()))
 
-    def rotate_heads(self, q, offset, cos, sin, rotated, meta, out, out_offset) -> None:
+    def rotate_heads(self, q, offset, cos, sin, rotated, meta, out, out_offset, pairing: int = 0) -> None:
         self._want(q, "q", (self.dtype,), 3)
         self._want(out, "rotated q", (self.dtype,), 3)
         self._want(cos, "cos table", (torch.float32,), 2)
@@ -717,34 +724,38 @@ class CudaOps(Ops):
         self._check(self.mix.fz_rotate_heads(_p(q), c_int(w), c_int(offset), _p(cos), _p(sin), c_int(rotated), _p(meta.pos),
                                              _p(meta.seq_row), _p(out), c_int(out.shape[2]), c_int(out_offset),
                                              c_int(_CODE[self.dtype]), c_int(n), c_int(heads), c_int(cos.shape[0]),
-                                             _p(self.err), self._stream()), "rotate_heads")
+                                             c_int(pairing), _p(self.err), self._stream()), "rotate_heads")
 
     def linear_heads(self, a, a_offset, k, w, out, out_offset) -> None:
         self._want(a, "per-head input", (self.dtype,), 3)
         self._want(w, "per-head weight", (self.dtype,), 3)
-        self._want(out, "per-head output", (self.dtype,), 3)
+        self._want(out, "per-head output", (self.dtype, torch.float32), 3)
         n, heads, wa = a.shape
         m = w.shape[1]
         if w.shape[0] != heads or w.shape[2] != k or a_offset + k > wa or out.shape[:2] != a.shape[:2] \
                 or out_offset + m > out.shape[2]:
             raise KernelError(f"linear_heads: a {tuple(a.shape)} from {a_offset}, w {tuple(w.shape)}, out {tuple(out.shape)} at {out_offset}")
-        es = a.element_size()
+        es, eo = a.element_size(), out.element_size()
         if self.use_tensor_cores and self.grouped_tensor_cores:
             args = (c_void_p(a.data_ptr() + a_offset * es), c_longlong(heads * wa), c_longlong(wa), _p(w),
-                    c_void_p(out.data_ptr() + out_offset * es), c_longlong(heads * out.shape[2]), c_longlong(out.shape[2]))
+                    c_void_p(out.data_ptr() + out_offset * eo), c_longlong(heads * out.shape[2]), c_longlong(out.shape[2]))
             if self.mix_tc.fz_grouped_tc_check(*args, c_int(m), c_int(k)) == 0:
-                self._check(self.mix_tc.fz_linear_heads_tc(*args, c_int(_CODE[self.dtype]), c_int(n), c_int(heads), c_int(m),
+                self._check(self.mix_tc.fz_linear_heads_tc(*args, c_int(_CODE[out.dtype]), c_int(n), c_int(heads), c_int(m),
                                                            c_int(k), self._stream()), "linear_heads (tensor cores)",
                             (n * heads * (k + m) + heads * m * k) * es)
                 return
         self._check(self.mix.fz_linear_heads(
             c_void_p(a.data_ptr() + a_offset * es), c_longlong(heads * wa), c_longlong(wa), _p(w),
-            c_void_p(out.data_ptr() + out_offset * es), c_longlong(heads * out.shape[2]), c_longlong(out.shape[2]),
-            c_int(_CODE[self.dtype]), c_int(_CODE[self.dtype]), c_int(n), c_int(heads), c_int(m), c_int(k), self._stream()),
+            c_void_p(out.data_ptr() + out_offset * eo), c_longlong(heads * out.shape[2]), c_longlong(out.shape[2]),
+            c_int(_CODE[self.dtype]), c_int(_CODE[out.dtype]), c_int(n), c_int(heads), c_int(m), c_int(k), self._stream()),
             "linear_heads", (n * heads * (k + m) + heads * m * k) * es)
 
-    def latent_attention(self, q, cache, meta, out, value_width, scale, window) -> None:
+    def latent_attention(self, q, cache, meta, out, value_width, scale, window, sink=None) -> None:
         self._want(q, "q", (self.dtype,), 3)
+        if sink is not None:
+            self._want(sink, "sinks", (torch.float32,), 1)
+            if sink.shape[0] != q.shape[1]:
+                raise KernelError(f"latent_attention: {tuple(sink.shape)} sinks for {q.shape[1]} heads")
         self._want(out, "attention output", (self.dtype,), 3)
         n, heads, width = q.shape
         if tuple(out.shape) != (n, heads, value_width):
@@ -770,14 +781,14 @@ class CudaOps(Ops):
                 _p(q), _p(pool), _p(meta.seq_row), _p(meta.seg), c_int(meta.n_segments), _p(table), c_int(table.shape[1]),
                 c_longlong(page_stride), c_int(cache.page_size), c_int(pool.shape[0]), _p(out), c_int(n), c_int(blocks),
                 c_int(heads), c_int(width), c_int(value_width), c_float(scale), c_int(window), c_int(splits), c_int(ctx),
-                _p(scratch), _p(self.err), self._stream()),
+                _p(scratch), _p(sink), _p(self.err), self._stream()),
                 "latent_attention (tensor cores)", nbytes)
             self.launches += 2 if splits > 1 else 1    # the kernel that zeroes rows of padding, the merge kernel
             return
         self._check(self.latent.fz_attn_latent(
             _p(q), _p(pool), _p(meta.pos), _p(meta.seq_row), _p(table), c_int(table.shape[1]), c_longlong(page_stride),
             c_int(cache.page_size), c_int(pool.shape[0]), _p(out), c_int(_CODE[self.dtype]), c_int(n), c_int(heads),
-            c_int(width), c_int(value_width), c_float(scale), c_int(window), _p(self.err), self._stream()),
+            c_int(width), c_int(value_width), c_float(scale), c_int(window), _p(sink), _p(self.err), self._stream()),
             "latent_attention", nbytes)
 
     # ---- experts chosen by a table
@@ -994,12 +1005,14 @@ class CudaOps(Ops):
             _p(self.err), self._stream()), "rotate_kv_write", n * need * (4 + q_out.element_size()))
 
     def sink_attention(self, q, cache, meta, out, num_heads, num_kv_heads, key_dim, value_dim, scale, window, keep_first, sink,
-                       softcap: float = 0.0, gate=None) -> None:
+                       softcap: float = 0.0, gate=None, span: int = 0) -> None:
         self._want(q, "q", (self.dtype,), 2)
         self._want(out, "attention output", (self.dtype,), 2)
         n = q.shape[0]
         if q.shape[1] != num_heads * key_dim or tuple(out.shape) != (n, num_heads * value_dim):
             raise KernelError(f"sink_attention: q {tuple(q.shape)}, out {tuple(out.shape)}")
+        if span < 0 or (span and keep_first):
+            raise KernelError(f"sink_attention: a chunked mask of {span} positions with {keep_first} kept first tokens")
         if sink is not None:
             self._want(sink, "sinks", (torch.float32,), 1)
             if sink.shape[0] != num_heads:
@@ -1015,7 +1028,8 @@ class CudaOps(Ops):
         table = meta.table(cache.group)
         nbytes = 0
         if self._profile is not None:
-            seen = sum(min(sg.pos0 + i + 1, (window + keep_first) if window else sg.pos0 + i + 1) for sg in meta.segments for i in range(sg.n))
+            seen = sum(min(sg.pos0 + i + 1, (window + keep_first) if window else sg.pos0 + i + 1, (sg.pos0 + i) % span + 1 if span else 1 << 62)
+                       for sg in meta.segments for i in range(sg.n))
             nbytes = seen * num_kv_heads * (key_dim + value_dim) * k.element_size() + n * num_heads * (key_dim + value_dim) * q.element_size()
         # A step of single tokens (bfloat16): a row's keys are cut into runs of chunks, one block each, and merged by a
         # second kernel, so that a few rows fill the GPU. Other steps: blocks of consecutive rows of a portion that share
@@ -1033,14 +1047,15 @@ class CudaOps(Ops):
                 c_int(table.shape[1]), c_longlong(k.stride(0)), c_longlong(k.stride(1)), c_longlong(k.stride(2)),
                 c_int(cache.page_size), c_int(k.shape[0]), _p(out), c_int(n), c_int(num_heads), c_int(num_kv_heads),
                 c_int(key_dim), c_float(scale), c_int(window), c_int(keep_first), _p(sink), c_float(softcap), _p(g), c_int(g_ld),
-                c_int(g_off), _p(self.err), self._stream()), "sink_attention (tensor cores)", nbytes)
+                c_int(g_off), c_int(span), _p(self.err), self._stream()), "sink_attention (tensor cores)", nbytes)
             return
         unit_chunks = units = 0
         part = None
         if self.split_decode_keys and self.dtype == torch.bfloat16 and max_portion == 1:
             ctx = max(1, int(meta.max_context))
-            unit_chunks = 2 if window else max(2, -(-ctx // (32 * self.sink_max_runs)))
-            units = int(self.seq.fz_sink_attention_units(c_int(window), c_int(keep_first), c_int(ctx), c_int(unit_chunks)))
+            reach = min(window or ctx, span or ctx)      # the most keys a row sees, kept first tokens aside
+            unit_chunks = 2 if window else max(2, -(-reach // (32 * self.sink_max_runs)))
+            units = int(self.seq.fz_sink_attention_units(c_int(window), c_int(keep_first), c_int(ctx), c_int(unit_chunks), c_int(span)))
             part = self._scratch("sink attention partials", n * num_heads * units * (value_dim + 2), torch.float32)
         self._check(self.seq.fz_sink_attention(
             _p(q), _p(k), _p(v), _p(meta.pos), _p(meta.seq_row), _p(meta.seg), c_int(getattr(meta, "max_segments", meta.n_segments)),
@@ -1048,7 +1063,7 @@ class CudaOps(Ops):
             c_longlong(k.stride(1)), c_longlong(k.stride(2)), c_int(cache.page_size), c_int(k.shape[0]), _p(out),
             c_int(_CODE[self.dtype]), c_int(n), c_int(num_heads), c_int(num_kv_heads), c_int(key_dim), c_int(value_dim),
             c_float(scale), c_int(window), c_int(keep_first), _p(sink), c_int(unit_chunks), c_int(units), _p(part),
-            c_float(softcap), _p(g), c_int(g_ld), c_int(g_off), _p(self.err), self._stream()), "sink_attention", nbytes)
+            c_float(softcap), _p(g), c_int(g_ld), c_int(g_off), c_int(span), _p(self.err), self._stream()), "sink_attention", nbytes)
         if units:
             self.launches += 1      # the merge kernel
 
@@ -1076,13 +1091,61 @@ class CudaOps(Ops):
     def activate(self, src, offset, kind, out) -> None:
         self._want(src, "activation input", (torch.float32,), 2)
         self._want(out, "activation output", (torch.float32, self.dtype), 2)
-        code = {"tanh": 0, "sigmoid": 1, "silu": 2, "gelu_tanh": 3}.get(kind)
+        code = _ACTIVATIONS.get(kind)
         n, w = out.shape
         if code is None or src.shape[0] != n or offset < 0 or offset + w > src.shape[1]:
             raise KernelError(f"activate: kind {kind!r}, src {tuple(src.shape)} from column {offset}, out {tuple(out.shape)}")
         self._check(self.rows.fz_activate(_p(src), c_int(src.shape[1]), c_int(offset), c_int(code), _p(out),
                                           c_int(_CODE[out.dtype]), c_int(n), c_int(w), self._stream()), "activate",
                     n * w * (4 + out.element_size()))
+
+    def gate_multiply(self, x, gate, gate_offset, kind, out) -> None:
+        self._want(x, "gated values", (self.dtype,), 2)
+        self._want(out, "gated output", (self.dtype,), 2)
+        self._want(gate, "gate", (torch.float32,), 2)
+        code = _ACTIVATIONS.get(kind)
+        n, w = x.shape
+        if code is None or out.shape != x.shape or gate.shape[0] != n or gate_offset < 0 or gate_offset + w > gate.shape[1]:
+            raise KernelError(f"gate_multiply: kind {kind!r}, x {tuple(x.shape)}, gate {tuple(gate.shape)} from column {gate_offset}")
+        self._check(self.rows.fz_gate_multiply(_p(x), _p(gate), c_int(gate.shape[1]), c_int(gate_offset), c_int(code), _p(out),
+                                               c_int(_CODE[self.dtype]), c_int(n), c_int(w), self._stream()), "gate_multiply",
+                    n * w * (4 + 2 * x.element_size()))
+
+    def blend_columns(self, dst, dst_offset, src, src_offset, width, weight) -> None:
+        self._want(dst, "blend target", (torch.float32,), 2)
+        self._want(src, "blend source", (torch.float32,), 2)
+        self._want(weight, "blend weight", (torch.float32,), 1)
+        n = dst.shape[0]
+        if src.shape[0] != n or dst_offset < 0 or dst_offset + width > dst.shape[1] or src_offset < 0 or \
+                src_offset + width > src.shape[1] or weight.numel() < 1:
+            raise KernelError(f"blend_columns: dst {tuple(dst.shape)} from {dst_offset}, src {tuple(src.shape)} from {src_offset}, width {width}")
+        self._check(self.rows.fz_blend_columns(_p(dst), c_int(dst.shape[1]), c_int(dst_offset), _p(src), c_int(src.shape[1]),
+                                               c_int(src_offset), _p(weight), c_int(n), c_int(width), self._stream()),
+                    "blend_columns", n * width * 12)
+
+    def rglru_scan(self, u, gates, gate_bias, lam, y, sharpness, state, meta, out) -> None:
+        self._want(u, "recurrence input", (self.dtype,), 2)
+        self._want(y, "gate branch", (self.dtype,), 2)
+        self._want(out, "recurrence output", (self.dtype,), 2)
+        self._want(gates, "gate inputs", (torch.float32,), 3)
+        self._want(gate_bias, "gate biases", (torch.float32,), 2)
+        self._want(lam, "decay parameter", (torch.float32,), 1)
+        self._want(state, "recurrent state", (torch.float32,), 2)
+        n, w = u.shape
+        parts = gates.shape[1]
+        if w % parts or tuple(gates.shape) != (n, parts, 2 * (w // parts)) or tuple(gate_bias.shape) != (parts, 2 * (w // parts)) or \
+                lam.shape[0] != w or y.shape != u.shape or out.shape != u.shape or state.shape[1] != w:
+            raise KernelError(f"rglru_scan: u {tuple(u.shape)}, gates {tuple(gates.shape)}, bias {tuple(gate_bias.shape)}, "
+                              f"lam {tuple(lam.shape)}, y {tuple(y.shape)}, state {tuple(state.shape)}")
+        # long portions: the recurrence's coefficients of all rows at once, then a scan of one multiply-add per token
+        cooked = int(getattr(meta, "max_portion", 0) or n) > RGLRU_COOK_ROWS
+        self._meta_rows = meta.seq_row
+        self._check(self.seq.fz_rglru_scan(_p(u), _p(gates), _p(gate_bias), _p(lam), _p(y), c_float(sharpness), _p(state),
+                                           _p(meta.seg), c_int(getattr(meta, "max_segments", meta.n_segments)), _p(meta.seq_row),
+                                           _p(out), c_int(_CODE[self.dtype]), c_int(n), c_int(w), c_int(parts), c_int(1 if cooked else 0),
+                                           self._stream()), "rglru_scan", n * w * (8 + 3 * u.element_size()))
+        if cooked:
+            self.launches += 1
 
     def hashed_pair_embed(self, table, token_ids, meta, state, buckets, mul_prev, mul_cur, x) -> None:
         self._want(table, "pair table", (torch.float32, torch.bfloat16), 2)
@@ -1167,7 +1230,7 @@ class CudaOps(Ops):
         self._meta_rows = meta.seq_row
         return self._sort_pairs(None, n, meta, choice, num_experts, align)
 
-    def moe_combine(self, terms, weights, shared, gate_logits, gate_column, out) -> None:
+    def moe_combine(self, terms, weights, shared, gate_logits, gate_column, out, add=None, scale: float = 1.0) -> None:
         self._want(terms, "expert terms", (torch.float32,), 2)
         self._want(weights, "router weights", (torch.float32,), 2)
         self._want(out, "feed-forward output", (torch.float32,), 2)
@@ -1178,10 +1241,20 @@ class CudaOps(Ops):
         ldg = 0
         if shared is not None:
             self._want(shared, "shared expert output", (torch.float32,), 2)
-            self._want(gate_logits, "shared gate logits", (torch.float32,), 2)
-            ldg = gate_logits.shape[1]
-            if shared.shape != out.shape or gate_logits.shape[0] != n or not 0 <= gate_column < ldg:
-                raise KernelError(f"moe_combine: shared {tuple(shared.shape)}, gate logits {tuple(gate_logits.shape)} column {gate_column}")
+            if shared.shape != out.shape:
+                raise KernelError(f"moe_combine: shared {tuple(shared.shape)}, out {tuple(out.shape)}")
+            if gate_logits is not None:
+                self._want(gate_logits, "shared gate logits", (torch.float32,), 2)
+                ldg = gate_logits.shape[1]
+                if gate_logits.shape[0] != n or not 0 <= gate_column < ldg:
+                    raise KernelError(f"moe_combine: gate logits {tuple(gate_logits.shape)} column {gate_column}")
+        else:
+            gate_logits = None
+        if add is not None:
+            self._want(add, "other term", (torch.float32,), 2)
+            if add.shape != out.shape:
+                raise KernelError(f"moe_combine: other term {tuple(add.shape)}, out {tuple(out.shape)}")
         self._check(self.seq.fz_moe_combine(_p(terms), _p(weights), c_int(top), _p(shared), _p(gate_logits), c_int(ldg),
-                                            c_int(gate_column), _p(self._step_rows(n)), _p(out), c_int(n), c_int(d), self._stream()),
-                    "moe_combine", n * d * 4 * (top + 1 + (shared is not None)))
+                                            c_int(gate_column), _p(self._step_rows(n)), _p(out), c_int(n), c_int(d), _p(add), c_float(scale),
+                                            self._stream()),
+                    "moe_combine", n * d * 4 * (top + 1 + (shared is not None) + (add is not None)))

@@ -4,7 +4,8 @@
 (fusezap/serve/models/llama.py:500-503, 508-523: `mean = sum * (1/D)`, the fused kernel also writes the residual
 stream). The residual stream x is float32 in both dtypes; the sum of squares, the scale and the weight product are
 computed in 32-bit and h is rounded once to the activation dtype. With `groups` > 1 the vector is normed in that many
-equal consecutive parts, each by its own mean square; the weight still spans the whole vector.
+equal consecutive parts, each by its own mean square; the weight still spans the whole vector. With `offset` the
+multiplier is `offset + w` (a weight stored as its distance from one has offset 1), added in float32 once at load.
 """
 from __future__ import annotations
 import torch
@@ -15,20 +16,25 @@ from .base import Norm, register_norm
 
 @register_norm("rmsnorm")
 class RMSNorm(Norm):
-    def __init__(self, size: int, eps: float, groups: int = 1, name: str = "weight", scalar: bool = False):
+    def __init__(self, size: int, eps: float, groups: int = 1, name: str = "weight", scalar: bool = False,
+                 offset: float = 0.0):
         """groups: the vector is split into this many equal consecutive parts and each is divided by its own root mean
         square (1: the whole vector). name: the weight's tensor name relative to the part ("" when the part's prefix is
-        the whole name). scalar: the weight is one number for all coordinates (a tensor without dimensions)."""
+        the whole name). scalar: the weight is one number for all coordinates (a tensor without dimensions). offset: the
+        row is multiplied by `offset + weight` (random weights are then drawn around zero)."""
         if groups <= 0 or size % groups:
             raise ValueError(f"a norm over {size} values cannot be split into {groups} equal groups")
         self.size, self.eps, self.groups, self.name, self.scalar = size, float(eps), int(groups), name, bool(scalar)
+        self.offset = float(offset)
         self.weight: torch.Tensor | None = None
 
     def tensors(self) -> dict[str, ParamSpec]:
-        return {self.name: ParamSpec(() if self.scalar else (self.size,), role="vector", init="ones")}
+        return {self.name: ParamSpec(() if self.scalar else (self.size,), role="vector", init="normal" if self.offset else "ones")}
 
     def bind(self, tensors, ops) -> None:
         self.weight = tensors[self.name]
+        if self.offset:
+            self.weight = (self.weight.float() + self.offset).contiguous()
         if self.scalar:      # the kernels take a weight per coordinate
             self.weight = self.weight.float().reshape(1).expand(self.size).contiguous()
 

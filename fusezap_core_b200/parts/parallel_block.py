@@ -89,3 +89,44 @@ class ParallelGatedBlock(Block):
         out = ws.get("block_delta", (n, self.D), torch.float32)
         ops.gated_sum(a, g1, f, g2, out, f_terms, f_weight)
         return x, out
+
+
+@register_block("parallel_shared")
+class ParallelSharedBlock(Block):
+    """`h = norm(x); x += m * (mixer(h) + ffn(h))`: one norm whose output both sublayers read, and one multiplier m
+    (`residual_mult`) on their sum. A layer without a feed-forward has `x += m * mixer(h)`. The pending term of the
+    layer before is added by the norm, in the same pass over the row; the sum and the product with m are 32-bit. A
+    feed-forward that can take the mixer's result and m into its own last kernel (`forward(ctx, h, add=, scale=)`, marked
+    by `takes_sum`) does so; otherwise the block adds the two terms up itself."""
+    def __init__(self, mixer: Mixer, ffn: FeedForward | None, make_norm, hidden_size: int, residual_mult: float = 1.0,
+                 norm=None, names: tuple = ("norm", "mixer", "ffn")):
+        self.mixer, self.ffn, self.D, self.mult = mixer, ffn, hidden_size, float(residual_mult)
+        self.names = tuple(names)
+        self.norm = make_norm(norm) if norm is not None else make_norm()
+
+    def children(self):
+        out = [(self.names[0], self.norm), (self.names[1], self.mixer)]
+        if self.ffn is not None:
+            out.append((self.names[2], self.ffn))
+        return tuple(out)
+
+    def tensors(self) -> dict[str, ParamSpec]:
+        return {(f"{prefix}.{k}" if k else prefix): v for prefix, part in self.children() for k, v in part.tensors().items()}
+
+    def bind(self, tensors, ops) -> None:
+        for prefix, part in self.children():
+            part.bind({k[len(prefix) + 1:]: v for k, v in tensors.items() if k == prefix or k.startswith(prefix + ".")}, ops)
+
+    def forward(self, ctx, x, delta, cache: LayerCache):
+        h = self.norm.forward(ctx, x, delta)                          # x += pending term; h = norm(x)
+        a = self.mixer.forward(ctx, h, cache)
+        if self.ffn is not None and getattr(self.ffn, "takes_sum", False):
+            return x, self.ffn.forward(ctx, h, add=a, scale=self.mult)
+        out = ctx.ws.get("block_delta", (x.shape[0], self.D), torch.float32)
+        if self.ffn is None:
+            if self.mult == 1.0:
+                return x, a
+            ctx.ops.weighted_sum([a], [self.mult], out)
+        else:
+            ctx.ops.weighted_sum([a, self.ffn.forward(ctx, h)], [self.mult, self.mult], out)
+        return x, out

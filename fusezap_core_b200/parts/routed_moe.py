@@ -8,6 +8,11 @@ no biases. A shared expert of the same form (`shared_size` > 0) runs for every t
 `sigmoid(W_sg h)`, one number per token. The step sorts its (row, choice) pairs by expert on the device and runs each
 expert's products over its own rows only; a row's result does not depend on the other rows. Router, softmax, weights
 and the weighted sum are 32-bit; the activation is computed from unrounded 32-bit sums.
+
+Options: `router_bias`: the logits are `W_router h + b` (tensor `<router_bias>`); `shared_gate=False`: the shared expert
+is added as it is, without a gate. With one group and `renormalize`, the weights are the softmax over the chosen logits
+alone (softmax over all, divided by the chosen ones' sum, is the same number). The part takes a block's other term and
+multiplier into its last kernel: `forward(ctx, h, add=a, scale=m)` returns `m * (a + ff(h))`.
 """
 from __future__ import annotations
 import math
@@ -19,13 +24,16 @@ from .base import FeedForward, register_feed_forward
 from .feed_forward import SwiGLU
 
 _NAMES = {"router": "router", "expert": "experts.{}", "gate": "gate_proj", "up": "up_proj", "down": "down_proj",
-          "shared": "shared_expert", "shared_gate": "shared_gate"}
+          "shared": "shared_expert", "shared_gate": "shared_gate", "router_bias": "router.bias"}
 
 
 @register_feed_forward("routed_moe")
 class RoutedMoE(FeedForward):
+    takes_sum = True      # forward(ctx, h, add=, scale=): see `ParallelSharedBlock`
+
     def __init__(self, hidden_size: int, intermediate_size: int, num_experts: int, top: int, groups: int = 1,
-                 keep_groups: int = 1, shared_size: int = 0, renormalize: bool = False, names: dict | None = None):
+                 keep_groups: int = 1, shared_size: int = 0, renormalize: bool = False, names: dict | None = None,
+                 router_bias: bool = False, shared_gate: bool = True):
         if not 0 < top <= num_experts:
             raise ValueError(f"top {top} must lie in 1..{num_experts}")
         if groups <= 0 or num_experts % groups or not 0 < keep_groups <= groups or top > keep_groups * (num_experts // groups):
@@ -33,6 +41,8 @@ class RoutedMoE(FeedForward):
         self.D, self.I, self.E, self.top = hidden_size, intermediate_size, num_experts, top
         self.groups, self.keep, self.renormalize = int(groups), int(keep_groups), bool(renormalize)
         self.names = {**_NAMES, **(names or {})}
+        self.router_bias, self.shared_gate = bool(router_bias), bool(shared_gate) and shared_size > 0
+        self.b_router = None
         self.shared = None
         if shared_size:
             n = self.names
@@ -52,9 +62,12 @@ class RoutedMoE(FeedForward):
             out[self._expert(e, "up")] = ParamSpec((self.I, self.D))
             out[self._expert(e, "down")] = ParamSpec((self.D, self.I))
         out[n["router"]] = ParamSpec((self.E, self.D))
+        if self.router_bias:
+            out[n["router_bias"]] = ParamSpec((self.E,), role="vector")
         if self.shared is not None:
             out.update({f"{n['shared']}.{k}": v for k, v in self.shared.tensors().items() if v.group is None})
-            out[f"{n['shared']}.{n['shared_gate']}"] = ParamSpec((1, self.D))
+            if self.shared_gate:
+                out[f"{n['shared']}.{n['shared_gate']}"] = ParamSpec((1, self.D))
         return out
 
     def bind(self, tensors, ops) -> None:
@@ -66,16 +79,20 @@ class RoutedMoE(FeedForward):
         if self.shared is not None:
             pre = n["shared"] + "."
             self.shared.bind({k[len(pre):]: v for k, v in tensors.items() if k.startswith(pre)}, ops)
-            router = torch.cat([router, tensors[pre + n["shared_gate"]]], 0)            # one product: [router; shared gate]
+            if self.shared_gate:
+                router = torch.cat([router, tensors[pre + n["shared_gate"]]], 0)        # one product: [router; shared gate]
         self.w_router = router.contiguous()
+        if self.router_bias:
+            b = tensors[n["router_bias"]].float()
+            self.b_router = torch.cat([b, b.new_zeros(router.shape[0] - self.E)]).contiguous()
 
     def weight_tensors(self) -> list:
         return [self.w_router, self.w_gate_up, self.w_down]
 
-    def forward(self, ctx, h: torch.Tensor) -> torch.Tensor:
+    def forward(self, ctx, h: torch.Tensor, add: torch.Tensor | None = None, scale: float = 1.0) -> torch.Tensor:
         n, ops, ws = h.shape[0], ctx.ops, ctx.ws
         z = ws.get("router_logits", (n, self.w_router.shape[0]), torch.float32)
-        ops.linear(h, self.w_router, None, z)
+        ops.linear(h, self.w_router, self.b_router, z)
         weights = ws.get("router_weights", (n, self.top), torch.float32)
         route = ops.route_by_scores(z, self.E, self.top, self.groups, self.keep, self.renormalize, ctx.meta, weights,
                                     math.gcd(self.D, self.I))
@@ -85,5 +102,9 @@ class RoutedMoE(FeedForward):
         ops.grouped_linear_scatter(y, self.w_down, route, terms)
         shared = self.shared.forward(ctx, h, tag="shared_") if self.shared is not None else None
         out = ws.get("moe_delta", (n, self.D), torch.float32)
-        ops.moe_combine(terms, weights, shared, z if shared is not None else None, self.E, out)
+        gate = z if self.shared_gate else None
+        if add is None and scale == 1.0:
+            ops.moe_combine(terms, weights, shared, gate, self.E, out)
+        else:
+            ops.moe_combine(terms, weights, shared, gate, self.E, out, add=add, scale=scale)
         return out

@@ -19,8 +19,13 @@ of key_dim values shared by the heads (`<q><norm_suffix>`, `<k><norm_suffix>`), 
 score s becomes `c * tanh(s / c)`; `head_gate`: head h's output is multiplied by `sigmoid(W_gate h)_h`, one number per
 head, before the output product; `own_kv=False`: the layer has no key and value projections and reads, with queries of
 its own, the cache that another layer's mixer wrote (its schedule entry names that cache slot); `cache_window`: the
-window the cache must keep when other layers read it too (None: this mixer's own). The norms, the temperature, the cap
-and the gate are 32-bit in both dtypes.
+window the cache must keep when other layers read it too (None: this mixer's own); `span` s > 0: a chunked causal mask,
+row i sees key j <= i only if `floor(i / s) = floor(j / s)`, blocks counted from position 0 of the sequence (with a
+window both must hold; the cache keeps every token); `value_mix`: "source" keeps this layer's values (the float32
+product, before they are rounded into the cache) for the step under `value_mix_key`, "blend" replaces this layer's
+values by `(1 - lam) v + lam v_source` of the same token before they are cached, with lam the layer's own number
+(tensor `<value_mix>`, which a source layer may carry and never reads). The norms, the temperature, the cap, the gate
+and the blend are 32-bit in both dtypes.
 """
 from __future__ import annotations
 import torch
@@ -30,7 +35,8 @@ from ..weights import ParamSpec
 from .base import LayerCache, Mixer, register_mixer
 from .retention import PAIRINGS
 
-_NAMES = {"q": "q_proj", "k": "k_proj", "v": "v_proj", "sink": "sinks", "out": "o_proj", "gate": "g_proj"}
+_NAMES = {"q": "q_proj", "k": "k_proj", "v": "v_proj", "sink": "sinks", "out": "o_proj", "gate": "g_proj",
+          "value_mix": "v_mix"}
 
 
 @register_mixer("sink_attention")
@@ -39,7 +45,8 @@ class SinkAttention(Mixer):
                  window: int = 0, keep_first: int = 0, sink: bool = True, rotated: int = 0, pairing: str = "neighbours",
                  position: str | None = None, names: dict | None = None, bias: tuple = (), bias_suffix: str = ".bias",
                  qk_norm: bool = False, norm_eps: float = 1e-6, norm_suffix: str = "_norm", query_temperature: tuple | None = None,
-                 softcap: float = 0.0, head_gate: bool = False, own_kv: bool = True, cache_window: int | None = None):
+                 softcap: float = 0.0, head_gate: bool = False, own_kv: bool = True, cache_window: int | None = None,
+                 span: int = 0, value_mix: str | None = None, value_mix_key: str = "first_values"):
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} query heads are not a multiple of {num_kv_heads} kv heads")
         if pairing not in PAIRINGS:
@@ -61,7 +68,13 @@ class SinkAttention(Mixer):
         self.cache_window = self.window if cache_window is None else int(cache_window)
         if self.cache_window and (not self.window or self.cache_window < self.window):
             raise ValueError(f"a cache that keeps {self.cache_window} tokens cannot serve a window of {self.window or 'all'}")
-        self.wqkv = self.bqkv = self.wo = self.bo = self.sink = self.q_norm_w = self.k_norm_w = None
+        self.span = int(span)
+        if self.span < 0 or (self.span and self.keep_first):
+            raise ValueError(f"a chunked mask of {span} positions: the size must be positive, and no first tokens are kept")
+        if value_mix not in (None, "source", "blend") or (value_mix and not own_kv):
+            raise ValueError(f"value_mix {value_mix!r} is not one of None, 'source', 'blend', or the layer has no values of its own")
+        self.value_mix, self.value_mix_key = value_mix, value_mix_key
+        self.wqkv = self.bqkv = self.wo = self.bo = self.sink = self.q_norm_w = self.k_norm_w = self.mix_w = None
 
     def tensors(self) -> dict[str, ParamSpec]:
         n = self.names
@@ -82,6 +95,8 @@ class SinkAttention(Mixer):
             out[n["gate"]] = ParamSpec((self.Hq, self.D))
         if self.has_sink:
             out[n["sink"]] = ParamSpec((self.Hq,), role="vector")
+        if self.value_mix is not None:
+            out[n["value_mix"]] = ParamSpec((), role="vector", ignore=self.value_mix == "source")
         return out
 
     def bind(self, tensors, ops) -> None:
@@ -102,6 +117,8 @@ class SinkAttention(Mixer):
         if self.qk_norm:
             self.q_norm_w = tensors[n["q"] + self.norm_suffix].float().contiguous()
             self.k_norm_w = tensors[n["k"] + self.norm_suffix].float().contiguous() if self.own_kv else None
+        if self.value_mix == "blend":
+            self.mix_w = tensors[n["value_mix"]].float().reshape(1).contiguous()
         ops.check_sink_attention(self.Hq, self.Hkv, self.dk, self.dv)
 
     def cache_need(self) -> KVNeed:
@@ -120,8 +137,20 @@ class SinkAttention(Mixer):
         if cache.write != self.own_kv:
             raise ValueError("a mixer with key and value projections of its own writes its cache slot, one without reads "
                              "another layer's: the schedule entry says otherwise")
-        qkv = ws.get("sink_qkv", (n, self.width), torch.float32)
+        # (a source of values for later layers keeps its product in a buffer that no other layer writes)
+        qkv = ws.get("sink_qkv" if self.value_mix != "source" else "sink_qkv:" + self.value_mix_key, (n, self.width), torch.float32)
         ops.linear(h, self.wqkv, self.bqkv, qkv)
+        if self.value_mix is not None:
+            off_v = (Hq + Hkv) * dk
+            if self.value_mix == "source":
+                ctx.shared[self.value_mix_key] = (qkv, off_v, Hkv * dv)
+            else:
+                if self.value_mix_key not in ctx.shared:
+                    raise ValueError(f"no earlier layer of this step left its values under {self.value_mix_key!r}")
+                src, src_off, src_w = ctx.shared[self.value_mix_key]
+                if src_w != Hkv * dv or src.shape[0] != n:
+                    raise ValueError(f"the values to blend with have another shape: {src_w} against {Hkv * dv} per row")
+                ops.blend_columns(qkv, off_v, src, src_off, Hkv * dv, self.mix_w)
         q = ws.get("sink_q", (n, Hq * dk), ops.dtype)
         pos = ctx.positions[self.position] if self.position is not None else None
         plain = not (self.qk_norm or self.q_temp or self.head_gate) and self.own_kv
@@ -133,7 +162,10 @@ class SinkAttention(Mixer):
                                 ctx.meta, cache, q, Hq, Hkv, dk, dv, q_norm=self.q_norm_w, k_norm=self.k_norm_w,
                                 norm_eps=self.norm_eps, query_temperature=self.q_temp)
         o = ws.get("sink_out", (n, Hq * dv), ops.dtype)
-        if self.softcap or self.head_gate:
+        if self.span:
+            ops.sink_attention(q, cache, ctx.meta, o, Hq, Hkv, dk, dv, self.scale, self.window, self.keep_first, self.sink,
+                               softcap=self.softcap, gate=(qkv, self.off_gate) if self.head_gate else None, span=self.span)
+        elif self.softcap or self.head_gate:
             ops.sink_attention(q, cache, ctx.meta, o, Hq, Hkv, dk, dv, self.scale, self.window, self.keep_first, self.sink,
                                softcap=self.softcap, gate=(qkv, self.off_gate) if self.head_gate else None)
         else:

@@ -552,3 +552,140 @@ class PlainOpsDeep(PlainOpsSeq):
         acc = acc + coef[depth + 1] * full
         self.add_rmsnorm(acc, None, weight, eps, h, rows)
         return True
+
+
+class PlainOpsGated(PlainOpsDeep):
+    """The operations of the real-gated recurrent unit, of the latent attention with paired neighbours, a sink and an
+    output gate, of the attention with a chunked mask and blended values, and of the feed-forward's sum with a block's
+    other term."""
+
+    def short_conv(self, h, w, state, meta, out, residual=True, activation=None, bias=None) -> None:
+        if bias is None:
+            return super().short_conv(h, w, state, meta, out, residual, activation)
+        taps = w.shape[1]
+        out.zero_()
+        for sg in meta.segments:
+            rows = h[sg.row0: sg.row0 + sg.n].float()
+            line = torch.cat([state[sg.state_slot] if taps > 1 else rows[:0], rows], 0)
+            z = torch.zeros_like(rows)
+            for j in range(taps):
+                z = z + w.float()[:, j] * line[j: j + sg.n]
+            z = z + bias.float() + (rows if residual else 0)
+            if activation == "silu":
+                z = z * torch.sigmoid(z)
+            out[sg.row0: sg.row0 + sg.n] = z.to(out.dtype)
+            if taps > 1:
+                state[sg.state_slot] = line[line.shape[0] - (taps - 1):]
+
+    def _turn_pairs(self, v, cos, sin, rotated, pos, pairing):
+        if pairing == 0:
+            return self._turn(v, cos, sin, rotated, pos)
+        c, s = cos[pos], sin[pos]
+        while c.dim() < v.dim():
+            c, s = c.unsqueeze(1), s.unsqueeze(1)
+        out = v.clone()
+        a, b = v[..., 0:rotated:2], v[..., 1:rotated:2]
+        out[..., 0:rotated:2], out[..., 1:rotated:2] = a * c - b * s, b * c + a * s
+        return out
+
+    def latent_cache_write(self, down, norm_weight, eps, cos, sin, rotated, meta, cache, pairing=0) -> None:
+        L = norm_weight.shape[0]
+        pos, row = meta.pos.long(), meta.seq_row.long()
+        c = down[:, :L]
+        c = c * torch.rsqrt((c * c).mean(-1, keepdim=True) + eps) * norm_weight.float()
+        e = torch.cat([c, self._turn_pairs(down[:, L:], cos, sin, rotated, pos, pairing)], -1).to(cache.keys.dtype)
+        table, bs = meta.table(cache.group), cache.page_size
+        for i in range(down.shape[0]):
+            if row[i] >= 0:
+                page = int(table[row[i], pos[i] // bs])
+                assert page >= 0, f"row {i} at position {int(pos[i])} has no page"
+                cache.keys[page, pos[i] % bs] = e[i]
+
+    def rotate_heads(self, q, offset, cos, sin, rotated, meta, out, out_offset, pairing=0) -> None:
+        v = self._turn_pairs(q[..., offset:].float(), cos, sin, rotated, meta.pos.long(), pairing)
+        v = torch.where((meta.seq_row >= 0)[:, None, None], v, torch.zeros(()))
+        out[..., out_offset: out_offset + v.shape[-1]] = v.to(out.dtype)
+
+    def latent_attention(self, q, cache, meta, out, value_width, scale, window, sink=None) -> None:
+        if sink is None:
+            return super().latent_attention(q, cache, meta, out, value_width, scale, window)
+        pos, row = meta.pos.long(), meta.seq_row.long()
+        table, bs = meta.table(cache.group), cache.page_size
+        out.zero_()
+        for i in range(q.shape[0]):
+            if row[i] < 0:
+                continue
+            p = int(pos[i])
+            js = torch.arange(max(0, p - window + 1) if window else 0, p + 1)
+            pages = table[row[i], js // bs].long()
+            assert (pages >= 0).all(), f"row {i}: a visible key's page was given back"
+            e = cache.keys[pages, js % bs].float()
+            s = torch.cat([(q[i].float() @ e.T) * scale, sink.float()[:, None]], -1)
+            out[i] = (torch.softmax(s, -1)[:, :-1] @ e[:, :value_width]).to(out.dtype)
+
+    def activate(self, src, offset, kind, out) -> None:
+        z = src[:, offset: offset + out.shape[1]].float()
+        out.copy_((z if kind == "identity" else self._act(z, kind)).to(out.dtype))
+
+    def gate_multiply(self, x, gate, gate_offset, kind, out) -> None:
+        z = gate[:, gate_offset: gate_offset + x.shape[1]].float()
+        out.copy_((x.float() * (z if kind == "identity" else self._act(z, kind))).to(out.dtype))
+
+    def blend_columns(self, dst, dst_offset, src, src_offset, width, weight) -> None:
+        w = weight.float()[0]
+        d = dst[:, dst_offset: dst_offset + width]
+        d.copy_((1.0 - w) * d + w * src[:, src_offset: src_offset + width])
+
+    def rglru_scan(self, u, gates, gate_bias, lam, y, sharpness, state, meta, out) -> None:
+        n, W = u.shape
+        bw = W // gates.shape[1]
+        g = gates.double() + gate_bias.double()
+        r = torch.sigmoid(g[..., :bw]).reshape(n, W)
+        i = torch.sigmoid(g[..., bw:]).reshape(n, W)
+        la = -sharpness * r * torch.nn.functional.softplus(lam.double())
+        a, b = torch.exp(la), torch.sqrt(-torch.expm1(2 * la)) * i * u.double()
+        out.zero_()
+        for sg in meta.segments:
+            S = state[sg.state_slot].double()
+            for t in range(sg.row0, sg.row0 + sg.n):
+                S = a[t] * S + b[t]
+                out[t] = (S * y[t].double()).to(out.dtype)
+            state[sg.state_slot] = S.float()
+
+    def sink_attention(self, q, cache, meta, out, num_heads, num_kv_heads, key_dim, value_dim, scale, window, keep_first, sink,
+                       softcap=0.0, gate=None, span=0):
+        if not span:
+            return super().sink_attention(q, cache, meta, out, num_heads, num_kv_heads, key_dim, value_dim, scale, window,
+                                          keep_first, sink, softcap, gate)
+        n, Hq, Hkv, dk, dv = q.shape[0], num_heads, num_kv_heads, key_dim, value_dim
+        pos, row = meta.pos.long(), meta.seq_row.long()
+        table, bs = meta.table(cache.group), cache.page_size
+        out.zero_()
+        for i in range(n):
+            if row[i] < 0:
+                continue
+            p = int(pos[i])
+            js = [j for j in range(p - p % span, p + 1) if not window or p - j < window]
+            pages = [int(table[row[i], j // bs]) for j in js]
+            assert min(pages) >= 0, "a visible key has no page"
+            K = torch.stack([cache.keys[pg, :, j % bs] for pg, j in zip(pages, js)]).float()
+            V = torch.stack([cache.values[pg, :, j % bs] for pg, j in zip(pages, js)]).float()
+            s = torch.einsum("gak,jgk->gaj", q[i].float().view(Hkv, Hq // Hkv, dk), K) * scale
+            if softcap:
+                s = softcap * torch.tanh(s / softcap)
+            if sink is not None:
+                s = torch.cat([s, sink.float().view(Hkv, Hq // Hkv, 1)], -1)
+            o = torch.einsum("gaj,jgv->gav", torch.softmax(s, -1)[..., :len(js)], V).reshape(Hq, dv)
+            if gate is not None:
+                g, off = gate
+                o = o * torch.sigmoid(g[i, off: off + Hq].float())[:, None]
+            out[i] = o.reshape(-1).to(out.dtype)
+
+    def moe_combine(self, terms, weights, shared, gate_logits, gate_column, out, add=None, scale=1.0) -> None:
+        n, top = weights.shape
+        acc = (terms.view(n, top, -1) * weights[:, :, None]).sum(1)
+        if shared is not None:
+            acc = acc + (torch.sigmoid(gate_logits[:, gate_column: gate_column + 1]) * shared if gate_logits is not None else shared)
+        if add is not None:
+            acc = acc + add
+        out.copy_(acc * scale)
