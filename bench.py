@@ -1,7 +1,7 @@
 """Benchmark: decode tokens per second of the Llama-3.1-8B-sized model (random bf16 weights) on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 4096] [--layers L] [--impl ours|reference]
-                    [--preset NAME] [--workload decode|stream|pepilix|gizulorn|nepudra]
+                    [--preset NAME] [--workload decode|stream|pepilix|gizulorn|nepudra|gimotar]
 
 A "step" is one decode step of `--batch` requests whose contexts end at `--context` tokens. Prints ONE JSON line:
   value      decoded tokens per second, timed on the device (CUDA events around K steps: metadata copy + graph replay)
@@ -29,6 +29,9 @@ a window and a sink beside the gated delta rule, routed experts with a shared on
 scores, a query temperature and head gates, layers that read an earlier layer's cache, windowed attention with normed and
 rotated heads, the generalized delta rule, depth-averaged layers, a hashed pair embedding) beside Gizulorn at equal width,
 layers, heads, window and dense feed-forward size.
+`--workload gimotar` (`--sizes m1024,m2048`, `--layers 4`) does the same for the Gimotar design (real-gated recurrent unit,
+latent attention with a sink and an output gate, attention under a chunked mask with blended values, routed experts with a
+shared expert in a parallel block), beside Gizulorn at equal sizes.
 `--workload pepilix` (`--sizes w1024,w2048`, `--layers 4`) times the Pepilix design beside the dense decoder at equal
 width, layers, heads, vocabulary and active feed-forward size: a 2,048-token prompt and decode steps at `--batch`
 requests through `LLMEngine.step()`, and (unless `--no-points`) a kernel-by-kernel profile of both; its line's `sizes`
@@ -160,7 +163,7 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--reference-device", default="CUDA", help="the reference's device name for --impl reference")
-    ap.add_argument("--workload", default="decode", choices=["decode", "stream", "pepilix", "gizulorn", "nepudra"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "stream", "pepilix", "gizulorn", "nepudra", "gimotar"],
                     help="pepilix: prefill and decode of the Pepilix design at a few layer sizes, beside the dense decoder "
                          "at equal width, layers, heads and active feed-forward size")
     ap.add_argument("--sizes", default="w1024,w2048", help="pepilix workload: which of its sizes to run")
@@ -194,6 +197,8 @@ def main() -> int:
         return design_workload(a, "gizulorn")
     if a.workload == "nepudra":
         return design_workload(a, "nepudra")
+    if a.workload == "gimotar":
+        return design_workload(a, "gimotar")
 
     import numpy as np
     import torch
@@ -487,6 +492,35 @@ def nepudra_configs(name: str, L: int, ctx: int):
     return nep, giz
 
 
+# Layer sizes for the Gimotar workload: (width, channels and gate parts of the recurrent unit, heads, unrotated, rotated, value
+# and latent size of the latent attention, heads, kv heads and head size of the chunked attention, chunk, experts, top,
+# expert ff, shared ff, vocab). Layers cycle through the recurrent unit, latent attention, and twice attention under a
+# chunked mask (the first keeps its values, the second blends with them); every layer has routed experts and a shared
+# expert. Gizulorn beside it (`GIZULORN_SIZES` of the same width) has the same width, layers, heads, experts, expert and
+# shared sizes and vocabulary, and a window as long as the chunk: each of Gimotar's kernels has a like kernel there (the
+# latent attention's is Pepilix's, the same kernel without the sink).
+GIMOTAR_SIZES = {
+    "m1024": (1024, 1024, 8, 8, 64, 64, 64, 256, 8, 2, 128, 512, 16, 2, 512, 512, 32768),
+    "m2048": (2048, 2048, 16, 16, 64, 64, 128, 512, 16, 4, 128, 1024, 32, 4, 512, 1024, 32768),
+}
+
+
+def gimotar_configs(name: str, L: int, ctx: int):
+    D, W, B, H, dn, dr, dv, rank, Ha, kv, hd, chunk, E, top, ff, shared, V = GIMOTAR_SIZES[name]
+    mlp = {"kind": "moe", "router": {"experts": E, "top": top}, "expert": {"ff": ff}, "shared": {"ff": shared}}
+    rec = {"width": W, "blocks": B, "conv": 4}
+    lat = {"heads": H, "dim": dn, "rot_dim": dr, "vdim": dv, "kv_rank": rank, "scale": (dn + dr) ** -0.5,
+           "rot": {"base": 10000.0, "dims": dr, "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}}
+    att = {"heads": Ha, "kv_heads": kv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "mask": {"size": chunk},
+           "rot": {"base": 250000.0, "dims": hd // 2}, "v_mix": True}
+    kinds = [("rglru", rec), ("latent_attention", lat), ("attention", att), ("attention", att)]
+    gim = {"architecture": "Gimotar", "vocab": V, "width": D, "norm": {"eps": 1e-6}, "residual_mult": 0.3,
+           "embedding": {"scale": D ** 0.5, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}},
+           "layers": [{"type": kinds[i % 4][0], "mixer": kinds[i % 4][1], "mlp": mlp} for i in range(L)]}
+    giz, _ = gizulorn_configs("g" + name[1:], L, ctx)
+    return gim, giz
+
+
 def pepilix_workload(a) -> int:
     return design_workload(a, "pepilix")
 
@@ -507,14 +541,16 @@ def design_workload(a, design: str) -> int:
     pk = peaks()
     rng = np.random.default_rng(5)
 
-    SIZES = {"pepilix": PEPILIX_SIZES, "gizulorn": GIZULORN_SIZES, "nepudra": NEPUDRA_SIZES}[design]
-    twin = "gizulorn" if design == "nepudra" else "dense"        # the model timed beside the design
+    SIZES = {"pepilix": PEPILIX_SIZES, "gizulorn": GIZULORN_SIZES, "nepudra": NEPUDRA_SIZES, "gimotar": GIMOTAR_SIZES}[design]
+    twin = "gizulorn" if design in ("nepudra", "gimotar") else "dense"        # the model timed beside the design
 
     def configs(name):
         if design == "gizulorn":
             return gizulorn_configs(name, L, ctx)
         if design == "nepudra":
             return nepudra_configs(name, L, ctx)
+        if design == "gimotar":
+            return gimotar_configs(name, L, ctx)
         D, H, dn, dr, dv, r, E, top, ff, V = PEPILIX_SIZES[name]
         mixer = {"heads": H, "dim": dn, "rot_dim": dr, "vdim": dv, "kv_rank": r, "scale": (dn + dr) ** -0.5,
                  "rot": {"base": 10000.0, "dims": dr}}
@@ -616,6 +652,9 @@ def design_workload(a, design: str) -> int:
                                          if design == "pepilix" else
                                          ("width", "heads", "kv_heads", "dim", "window", "delta_heads", "delta_dim", "ff", "vocab")
                                          if design == "nepudra" else
+                                         ("width", "rglru_width", "rglru_blocks", "latent_heads", "dim", "rot_dim", "vdim", "kv_rank",
+                                          "heads", "kv_heads", "head_dim", "chunk", "experts", "top", "ff", "shared_ff", "vocab")
+                                         if design == "gimotar" else
                                          ("width", "heads", "dim", "vdim", "kv_heads", "window", "key_heads", "experts", "top", "groups",
                                           "keep", "ff", "shared_ff", "vocab"), SIZES[n])) for n in sizes},
                    "beside": twin,

@@ -41,7 +41,7 @@ def add_engine_options(s: argparse.ArgumentParser) -> None:
 
 
 def build_parser() -> argparse.ArgumentParser:
-    ap = argparse.ArgumentParser(prog="fusezap_core_b200", description="B200-native engine for the dense Llama / Qwen2.5 decoder, for Pepilix and for Gizulorn")
+    ap = argparse.ArgumentParser(prog="fusezap_core_b200", description="B200-native engine for the dense Llama / Qwen2.5 decoder, for Pepilix, Gizulorn, Nepudra and Gimotar")
     sub = ap.add_subparsers(dest="cmd", required=True)
     g = sub.add_parser("generate", help="generate tokens for prompts given as token ids")
     g.add_argument("model", nargs="?", default=None, help="model folder (config.json + safetensors)")
