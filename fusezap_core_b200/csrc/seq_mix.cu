@@ -1035,8 +1035,9 @@ router_topk_kernel(const float* __restrict__ logits, int ld, int N, int E, int t
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n = blockIdx.x * ROUTER_WARPS + warp;
   if (n >= N) return;
-  float* s = smem + (size_t)warp * (E + groups);
+  float* s = smem + (size_t)warp * (E + groups + top);
   float* gmax = s + E;
+  float* picked = gmax + groups;                       // the chosen scores, until their sum is known
   if (seq_row[n] < 0) {
     for (int k = lane; k < top; k += 32) { choice[(size_t)n * top + k] = 0; weight[(size_t)n * top + k] = 0.f; }
     return;
@@ -1084,12 +1085,11 @@ router_topk_kernel(const float* __restrict__ logits, int ld, int N, int E, int t
         bv = 0.f;
       }
       choice[(size_t)n * top + k] = best;
-      weight[(size_t)n * top + k] = bv;
+      picked[k] = bv;
       total += bv;
       s[best] = -1.f;
     }
-    if (renorm)
-      for (int k = 0; k < top; ++k) weight[(size_t)n * top + k] = __fdiv_rn(weight[(size_t)n * top + k], total);
+    for (int k = 0; k < top; ++k) weight[(size_t)n * top + k] = renorm ? __fdiv_rn(picked[k], total) : picked[k];
   }
 }
 
@@ -1125,7 +1125,8 @@ moe_combine_kernel(const float* __restrict__ terms, const float* __restrict__ w,
 //
 // Long portions run in two launches: `rglru_cook_kernel` (every (row, channel) on its own) overwrites the two gate
 // inputs by a and b = sqrt(1 - a^2) i u, and the scan, a thread per (portion, channel), walks the portion's tokens with
-// one fused multiply-add each, sixteen tokens' loads in flight. Steps of short portions (decoded tokens) run the scan
+// one fused multiply-add each, sixteen tokens' loads in flight. What bounds it is how many loads the SMs in use keep in
+// flight, so a long portion's channels are spread over as many SMs as there are half warps of channels. Steps of short portions (decoded tokens) run the scan
 // alone, which then cooks a and b itself.
 __device__ __forceinline__ float rglru_softplus(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
 __device__ __forceinline__ void rglru_cook(float gr, float gi, float br, float bi, float k, float u, float& a, float& b) {
@@ -1155,7 +1156,6 @@ rglru_cook_kernel(const T* __restrict__ u, float* __restrict__ gates, const floa
   }
 }
 
-constexpr int RGLRU_AHEAD = 16;
 template <typename T, bool COOKED>
 __global__ void __launch_bounds__(64)
 rglru_scan_kernel(const T* __restrict__ u, const float* __restrict__ gates, const float* __restrict__ gbias,
@@ -1179,6 +1179,7 @@ rglru_scan_kernel(const T* __restrict__ u, const float* __restrict__ gates, cons
   fz_grid_wait();
   if (c >= W || cnt <= 0 || slot < 0) return;
   float S = state[(size_t)slot * W + c];
+  constexpr int RGLRU_AHEAD = 16;      // tokens whose loads are in flight at once
   for (int t0 = 0; t0 < cnt; t0 += RGLRU_AHEAD) {
     float a[RGLRU_AHEAD], b[RGLRU_AHEAD], yy[RGLRU_AHEAD];
 #pragma unroll
@@ -1201,6 +1202,97 @@ rglru_scan_kernel(const T* __restrict__ u, const float* __restrict__ gates, cons
     }
   }
   state[(size_t)slot * W + c] = S;
+}
+
+// The scan of long portions where the channels pair up (W and W / B even): a thread owns two neighbouring channels, and
+// the coefficients and gate values of the next 32 or 48 tokens travel into the thread's own places in a ring of stages
+// in shared memory (`cp.async`, 8 and 4 bytes) while the sixteen in hand are walked, so a thread waits for memory once
+// per portion, not once per sixteen tokens. A thread reads only what it copied itself: `cp.async.wait_group` orders that, no barrier
+// is needed. Same arithmetic and bits as `rglru_scan_kernel<T, true>`.
+template <typename T> struct PairOf;
+template <> struct PairOf<float> { using type = float2; static __device__ __forceinline__ float2 f(float2 v) { return v; } };
+template <> struct PairOf<__nv_bfloat16> {
+  using type = __nv_bfloat162;
+  static __device__ __forceinline__ float2 f(__nv_bfloat162 v) { return __bfloat1622float2(v); }
+};
+__device__ __forceinline__ void cp_async8(void* dst, const void* src) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(d), "l"(src) : "memory");
+}
+template <int N> __device__ __forceinline__ void cp_async_wait_n() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void store_pair(float* p, float x, float y) { *(float2*)p = make_float2(x, y); }
+__device__ __forceinline__ void store_pair(__nv_bfloat16* p, float x, float y) { *(__nv_bfloat162*)p = __floats2bfloat162_rn(x, y); }
+
+constexpr int RGLRU_STAGE = 16, RGLRU_PAIR_THREADS = 32;
+template <typename T>
+__global__ void __launch_bounds__(RGLRU_PAIR_THREADS)
+rglru_scan_pairs_kernel(const float* __restrict__ gates, const T* __restrict__ y, float* __restrict__ state,
+                        const int* __restrict__ seg, T* __restrict__ out, int W, int bw) {
+  fz_grid_launch_dependents();
+  using P = typename PairOf<T>::type;
+  constexpr int NST = sizeof(P) == 8 ? 3 : 4;      // stages of the ring (what fits in 48 KB of shared memory)
+  __shared__ __align__(16) float2 sa[NST][RGLRU_STAGE][RGLRU_PAIR_THREADS], sb[NST][RGLRU_STAGE][RGLRU_PAIR_THREADS];
+  __shared__ __align__(16) P sy[NST][RGLRU_STAGE][RGLRU_PAIR_THREADS];
+  const int s = blockIdx.x, tid = threadIdx.x;
+  const int c = 2 * (blockIdx.y * RGLRU_PAIR_THREADS + tid);
+  const int row0 = seg[4 * s], cnt = seg[4 * s + 1], slot = seg[4 * s + 3];
+  fz_grid_wait();
+  if (c >= W || cnt <= 0 || slot < 0) return;
+  const int part = c / bw, gcol = part * 2 * bw + (c - part * bw);
+  // (pointers walk from token to token by a fixed stride; a stage that lies wholly inside the portion has no tests)
+  const size_t g_step = (size_t)2 * W, y_step = (size_t)W;
+  const float* g_next = gates + (size_t)row0 * g_step + gcol;
+  const T* y_next = y + (size_t)row0 * y_step + c;
+  int t_next = 0;
+  auto issue = [&](int st) {
+    if (t_next + RGLRU_STAGE <= cnt) {
+#pragma unroll
+      for (int i = 0; i < RGLRU_STAGE; ++i) {
+        cp_async8(&sa[st][i][tid], g_next + i * g_step);
+        cp_async8(&sb[st][i][tid], g_next + i * g_step + bw);
+        if (sizeof(P) == 8) cp_async8(&sy[st][i][tid], y_next + i * y_step);
+        else cp_async4(&sy[st][i][tid], y_next + i * y_step);
+      }
+    } else {
+      for (int i = 0; t_next + i < cnt; ++i) {
+        cp_async8(&sa[st][i][tid], g_next + i * g_step);
+        cp_async8(&sb[st][i][tid], g_next + i * g_step + bw);
+        if (sizeof(P) == 8) cp_async8(&sy[st][i][tid], y_next + i * y_step);
+        else cp_async4(&sy[st][i][tid], y_next + i * y_step);
+      }
+    }
+    cp_async_commit();                       // (past the portion's end: an empty group)
+    t_next += RGLRU_STAGE;
+    g_next += RGLRU_STAGE * g_step;
+    y_next += RGLRU_STAGE * y_step;
+  };
+  float S0 = state[(size_t)slot * W + c], S1 = state[(size_t)slot * W + c + 1];
+#pragma unroll
+  for (int k = 0; k < NST - 1; ++k) issue(k);
+  int st = 0;
+  T* o = out + (size_t)row0 * y_step + c;
+  for (int t0 = 0; t0 < cnt; t0 += RGLRU_STAGE, st = st + 1 == NST ? 0 : st + 1, o += RGLRU_STAGE * y_step) {
+    issue(st == 0 ? NST - 1 : st - 1);
+    cp_async_wait_n<NST - 1>();              // this stage's group has landed
+    if (t0 + RGLRU_STAGE <= cnt) {
+#pragma unroll
+      for (int i = 0; i < RGLRU_STAGE; ++i) {
+        const float2 a = sa[st][i][tid], b = sb[st][i][tid], yy = PairOf<T>::f(sy[st][i][tid]);
+        S0 = __fmaf_rn(a.x, S0, b.x);
+        S1 = __fmaf_rn(a.y, S1, b.y);
+        store_pair(o + i * y_step, __fmul_rn(S0, yy.x), __fmul_rn(S1, yy.y));
+      }
+    } else {
+      for (int i = 0; t0 + i < cnt; ++i) {
+        const float2 a = sa[st][i][tid], b = sb[st][i][tid], yy = PairOf<T>::f(sy[st][i][tid]);
+        S0 = __fmaf_rn(a.x, S0, b.x);
+        S1 = __fmaf_rn(a.y, S1, b.y);
+        store_pair(o + i * y_step, __fmul_rn(S0, yy.x), __fmul_rn(S1, yy.y));
+      }
+    }
+  }
+  state[(size_t)slot * W + c] = S0;
+  state[(size_t)slot * W + c + 1] = S1;
 }
 
 struct Terms {
@@ -1481,7 +1573,7 @@ FZ_API int fz_router_topk(const float* logits, int ld, int N, int E, int top, in
   if (N <= 0) return FZ_OK;
   if (E <= 0 || E > 2048 || top <= 0 || top > E || groups <= 0 || E % groups || keep <= 0 || keep > groups ||
       top > keep * (E / groups)) return FZ_BAD_SHAPE;
-  const size_t smem = sizeof(float) * ROUTER_WARPS * (size_t)(E + groups);
+  const size_t smem = sizeof(float) * ROUTER_WARPS * (size_t)(E + groups + top);
   fz_launch(router_topk_kernel, dim3((N + ROUTER_WARPS - 1) / ROUTER_WARPS), dim3(32 * ROUTER_WARPS), smem, stream, logits, ld,
             N, E, top, groups, keep, renorm, seq_row, choice, weight);
   FZ_LAUNCH_CHECK();
@@ -1506,7 +1598,10 @@ FZ_API int fz_rglru_scan(const void* u, float* gates, const float* gbias, const 
   if (W <= 0 || B <= 0 || W % B || n_seg > 65535 * 32) return FZ_BAD_SHAPE;
   if (dtype != FZ_F32 && dtype != FZ_BF16) return FZ_BAD_DTYPE;
   const int bw = W / B;
-  const dim3 grid(n_seg, (W + 63) / 64);
+  // long portions (few of them in a step): blocks of 32 or 16 channels until the channels alone fill the SMs
+  int tpb = 64;
+  while (cooked && tpb > 16 && (W + tpb - 1) / tpb < 148) tpb >>= 1;
+  const dim3 grid(n_seg, (W + tpb - 1) / tpb);
   if (cooked) {
     const long long total = (long long)N * W;
     long long blocks = (total + 255) / 256;
@@ -1516,10 +1611,20 @@ FZ_API int fz_rglru_scan(const void* u, float* gates, const float* gbias, const 
     else
       fz_launch(rglru_cook_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(256), 0, stream, (const __nv_bfloat16*)u, gates, gbias, lam, sharp, seq_row, W, bw, total);
     FZ_LAUNCH_CHECK();
+    if (W % 2 == 0 && bw % 2 == 0 && (((uintptr_t)gates | (uintptr_t)y | (uintptr_t)out) & 15) == 0) {
+      const dim3 pgrid(n_seg, (W / 2 + RGLRU_PAIR_THREADS - 1) / RGLRU_PAIR_THREADS);
+      if (dtype == FZ_F32)
+        fz_launch(rglru_scan_pairs_kernel<float>, pgrid, dim3(RGLRU_PAIR_THREADS), 0, stream, gates, (const float*)y, state, seg, (float*)out, W, bw);
+      else
+        fz_launch(rglru_scan_pairs_kernel<__nv_bfloat16>, pgrid, dim3(RGLRU_PAIR_THREADS), 0, stream, gates, (const __nv_bfloat16*)y, state, seg,
+                  (__nv_bfloat16*)out, W, bw);
+      FZ_LAUNCH_CHECK();
+      return FZ_OK;
+    }
     if (dtype == FZ_F32)
-      fz_launch(rglru_scan_kernel<float, true>, grid, dim3(64), 0, stream, (const float*)u, gates, gbias, lam, (const float*)y, sharp, state, seg, (float*)out, W, bw);
+      fz_launch(rglru_scan_kernel<float, true>, grid, dim3(tpb), 0, stream, (const float*)u, gates, gbias, lam, (const float*)y, sharp, state, seg, (float*)out, W, bw);
     else
-      fz_launch(rglru_scan_kernel<__nv_bfloat16, true>, grid, dim3(64), 0, stream, (const __nv_bfloat16*)u, gates, gbias, lam, (const __nv_bfloat16*)y, sharp, state, seg, (__nv_bfloat16*)out, W, bw);
+      fz_launch(rglru_scan_kernel<__nv_bfloat16, true>, grid, dim3(tpb), 0, stream, (const __nv_bfloat16*)u, gates, gbias, lam, (const __nv_bfloat16*)y, sharp, state, seg, (__nv_bfloat16*)out, W, bw);
   } else {
     if (dtype == FZ_F32)
       fz_launch(rglru_scan_kernel<float, false>, grid, dim3(64), 0, stream, (const float*)u, gates, gbias, lam, (const float*)y, sharp, state, seg, (float*)out, W, bw);

@@ -165,6 +165,71 @@ activate_kernel(const float* __restrict__ src, int ld, int off, int kind, T* __r
   }
 }
 
+__device__ __forceinline__ float act_of(float z, int kind) {
+  if (kind == 0) return tanhf(z);
+  if (kind == 1) return 1.0f / (1.0f + expf(-z));
+  if (kind == 2) return z / (1.0f + expf(-z));
+  if (kind == 3) return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  return z;
+}
+__device__ __forceinline__ void st4(float* d, float4 v) { *(float4*)d = v; }
+__device__ __forceinline__ void st4(__nv_bfloat16* d, float4 v) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  *(uint2*)d = make_uint2(*(const uint32_t*)&lo, *(const uint32_t*)&hi);
+}
+__device__ __forceinline__ float4 ld4(const float* p) { return *(const float4*)p; }
+__device__ __forceinline__ float4 ld4(const __nv_bfloat16* p) {
+  const uint2 u = *(const uint2*)p;
+  const float2 a = __bfloat1622float2(*(const __nv_bfloat162*)&u.x), b = __bfloat1622float2(*(const __nv_bfloat162*)&u.y);
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+
+// The three kernels below with four columns per thread (16-byte loads of the float32 operands), for widths, offsets and
+// row pitches that are multiples of four and 16-byte aligned bases: the same values as one column per thread.
+template <typename T>
+__global__ void __launch_bounds__(256)
+activate_vec_kernel(const float* __restrict__ src, int ld, int off, int kind, T* __restrict__ out, int W, long long quads) {
+  fz_grid_launch_dependents();
+  fz_grid_wait();
+  const int wq = W >> 2;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < quads; idx += (long long)gridDim.x * blockDim.x) {
+    const long long n = idx / wq;
+    const int j = (int)(idx - n * wq) << 2;
+    const float4 z = ld4(src + n * ld + off + j);
+    st4(out + n * W + j, make_float4(act_of(z.x, kind), act_of(z.y, kind), act_of(z.z, kind), act_of(z.w, kind)));
+  }
+}
+template <typename T>
+__global__ void __launch_bounds__(256)
+gate_multiply_vec_kernel(const T* x, const float* __restrict__ gate, int ld, int off, int kind, T* out, int W, long long quads) {
+  fz_grid_launch_dependents();
+  fz_grid_wait();
+  const int wq = W >> 2;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < quads; idx += (long long)gridDim.x * blockDim.x) {
+    const long long n = idx / wq;
+    const int j = (int)(idx - n * wq) << 2;
+    const float4 z = ld4(gate + n * ld + off + j), v = ld4(x + n * W + j);
+    st4(out + n * W + j, make_float4(__fmul_rn(v.x, act_of(z.x, kind)), __fmul_rn(v.y, act_of(z.y, kind)),
+                                     __fmul_rn(v.z, act_of(z.z, kind)), __fmul_rn(v.w, act_of(z.w, kind))));
+  }
+}
+__global__ void __launch_bounds__(256)
+blend_columns_vec_kernel(float* __restrict__ dst, int ldd, int doff, const float* __restrict__ src, int lds, int soff,
+                         const float* __restrict__ weight, int W, long long quads) {
+  fz_grid_launch_dependents();
+  const float w = weight[0], keep = __fsub_rn(1.0f, w);
+  fz_grid_wait();
+  const int wq = W >> 2;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < quads; idx += (long long)gridDim.x * blockDim.x) {
+    const long long n = idx / wq;
+    const int j = (int)(idx - n * wq) << 2;
+    float* d = dst + n * ldd + doff + j;
+    const float4 a = ld4(d), b = ld4(src + n * lds + soff + j);
+    st4(d, make_float4(__fadd_rn(__fmul_rn(keep, a.x), __fmul_rn(w, b.x)), __fadd_rn(__fmul_rn(keep, a.y), __fmul_rn(w, b.y)),
+                       __fadd_rn(__fmul_rn(keep, a.z), __fmul_rn(w, b.z)), __fadd_rn(__fmul_rn(keep, a.w), __fmul_rn(w, b.w))));
+  }
+}
+
 // out = T(x * act(gate[:, off + j])): the activation (kinds of `activate_kernel`) and the product in float32. out may be x.
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -175,13 +240,7 @@ gate_multiply_kernel(const T* x, const float* __restrict__ gate, int ld, int off
     const long long n = idx / W;
     const int j = (int)(idx - n * W);
     const float z = gate[n * ld + off + j];
-    float v;
-    if (kind == 0) v = tanhf(z);
-    else if (kind == 1) v = 1.0f / (1.0f + expf(-z));
-    else if (kind == 2) v = z / (1.0f + expf(-z));
-    else if (kind == 3) v = 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
-    else v = z;
-    out[idx] = Cvt<T>::from_f(__fmul_rn(Cvt<T>::to_f(x[idx]), v));
+    out[idx] = Cvt<T>::from_f(__fmul_rn(Cvt<T>::to_f(x[idx]), act_of(z, kind)));
   }
 }
 
@@ -261,6 +320,15 @@ FZ_API int fz_activate(const float* src, int ld, int off, int kind, void* out, i
   const long long total = (long long)N * W;
   if (total <= 0) return FZ_OK;
   if (kind < 0 || kind > 4 || off < 0 || off + W > ld) return FZ_BAD_SHAPE;
+  if (W % 4 == 0 && off % 4 == 0 && ld % 4 == 0 && (((uintptr_t)src | (uintptr_t)out) & 15) == 0 && (dtype == FZ_F32 || dtype == FZ_BF16)) {
+    const long long quads = total / 4;
+    long long vb = (quads + 255) / 256;
+    if (vb > 148LL * 16) vb = 148LL * 16;
+    if (dtype == FZ_F32) fz_launch(activate_vec_kernel<float>, dim3((int)vb), dim3(256), 0, stream, src, ld, off, kind, (float*)out, W, quads);
+    else fz_launch(activate_vec_kernel<__nv_bfloat16>, dim3((int)vb), dim3(256), 0, stream, src, ld, off, kind, (__nv_bfloat16*)out, W, quads);
+    FZ_LAUNCH_CHECK();
+    return FZ_OK;
+  }
   long long blocks = (total + 255) / 256;
   if (blocks > 148LL * 16) blocks = 148LL * 16;
   if (dtype == FZ_F32) fz_launch(activate_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, src, ld, off, kind, (float*)out, W, total);
@@ -276,6 +344,19 @@ FZ_API int fz_gate_multiply(const void* x, const float* gate, int ld, int off, i
   const long long total = (long long)N * W;
   if (total <= 0) return FZ_OK;
   if (kind < 0 || kind > 4 || off < 0 || off + W > ld) return FZ_BAD_SHAPE;
+  if (W % 4 == 0 && off % 4 == 0 && ld % 4 == 0 && (((uintptr_t)x | (uintptr_t)gate | (uintptr_t)out) & 15) == 0 &&
+      (dtype == FZ_F32 || dtype == FZ_BF16)) {
+    const long long quads = total / 4;
+    long long vb = (quads + 255) / 256;
+    if (vb > 148LL * 16) vb = 148LL * 16;
+    if (dtype == FZ_F32)
+      fz_launch(gate_multiply_vec_kernel<float>, dim3((int)vb), dim3(256), 0, stream, (const float*)x, gate, ld, off, kind, (float*)out, W, quads);
+    else
+      fz_launch(gate_multiply_vec_kernel<__nv_bfloat16>, dim3((int)vb), dim3(256), 0, stream, (const __nv_bfloat16*)x, gate, ld, off, kind,
+                (__nv_bfloat16*)out, W, quads);
+    FZ_LAUNCH_CHECK();
+    return FZ_OK;
+  }
   long long blocks = (total + 255) / 256;
   if (blocks > 148LL * 16) blocks = 148LL * 16;
   if (dtype == FZ_F32)
@@ -293,6 +374,14 @@ FZ_API int fz_blend_columns(float* dst, int ldd, int doff, const float* src, int
   const long long total = (long long)N * W;
   if (total <= 0) return FZ_OK;
   if (doff < 0 || doff + W > ldd || soff < 0 || soff + W > lds || weight == nullptr) return FZ_BAD_SHAPE;
+  if (W % 4 == 0 && doff % 4 == 0 && ldd % 4 == 0 && soff % 4 == 0 && lds % 4 == 0 && (((uintptr_t)dst | (uintptr_t)src) & 15) == 0) {
+    const long long quads = total / 4;
+    long long vb = (quads + 255) / 256;
+    if (vb > 148LL * 16) vb = 148LL * 16;
+    fz_launch(blend_columns_vec_kernel, dim3((int)vb), dim3(256), 0, stream, dst, ldd, doff, src, lds, soff, weight, W, quads);
+    FZ_LAUNCH_CHECK();
+    return FZ_OK;
+  }
   long long blocks = (total + 255) / 256;
   if (blocks > 148LL * 16) blocks = 148LL * 16;
   fz_launch(blend_columns_kernel, dim3((int)blocks), dim3(256), 0, stream, dst, ldd, doff, src, lds, soff, weight, W, total);
