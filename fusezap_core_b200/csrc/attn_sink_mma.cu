@@ -33,15 +33,18 @@ sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
   const uint32_t s_base = smem_u32(smem);          // [2 stages][K | V], then Q
   const uint32_t s_q = s_base + 4 * TILE_BYTES;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int h = blockIdx.z;
+  // grid (portions + 1, heads, row tiles): blocks are handed out with the tile index falling, so a portion's last
+  // tiles, which have the most keys behind them under a causal or chunked mask, start first and the short ones fill
+  // the tail
+  const int h = blockIdx.y, tile = (int)(gridDim.z - 1 - blockIdx.z);
   if (blockIdx.x == gridDim.x - 1) {               // rows of padding get zeros
-    if (blockIdx.y == 0)
+    if (tile == 0)
       for (int n = 0; n < N; ++n)
         if (seq_row[n] < 0)
           for (int i = tid; i < HD; i += THREADS) out[((size_t)n * Hq + h) * HD + i] = __float2bfloat16_rn(0.f);
     return;
   }
-  const int s_idx = blockIdx.x, r_off = BM * (int)blockIdx.y;
+  const int s_idx = blockIdx.x, r_off = BM * tile;
   const int row0 = seg[4 * s_idx], n_rows = seg[4 * s_idx + 1], pos0 = seg[4 * s_idx + 2];
   if (r_off >= n_rows) return;
   const int kvh = h / (Hq / Hkv);
@@ -222,7 +225,7 @@ int launch(const void* q, const void* k_pool, const void* v_pool, const int* seg
   }
   const int tiles = (max_portion + BM - 1) / BM;
   if (tiles > 65535 || Hq > 65535) return FZ_TOO_LARGE;
-  fz_launch(sink_attention_mma_kernel<HD>, dim3(n_seg + 1, tiles, Hq), dim3(THREADS), smem, stream, (const __nv_bfloat16*)q,
+  fz_launch(sink_attention_mma_kernel<HD>, dim3(n_seg + 1, Hq, tiles), dim3(THREADS), smem, stream, (const __nv_bfloat16*)q,
             (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, seg, seq_row, table, mb, page_stride, head_stride,
             tok_stride, page_size, n_pages, (__nv_bfloat16*)out, Hq, Hkv, scale * LOG2E, window, keep_first, sink,
             softcap > 0.f ? softcap * LOG2E : 0.f, softcap > 0.f ? scale / softcap : 0.f, gate, gate_ld, gate_off, N, err,
