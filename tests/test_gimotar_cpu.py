@@ -137,6 +137,16 @@ def test_the_first_blending_layers_own_weight_is_not_read(dirs, tmp_path):
     assert rel_rms(run_cut(runner, cache, "r", toks, (20,)), plain_logits(cfg, dirs["mix"][2], toks)) < 2e-5
 
 
+def test_a_strong_blend_of_values_shows_in_the_logits(tmp_path):
+    d, cfg, w = make_dir("mix", tmp_path, change=lambda t: t.update({"l3.mix.vmix": torch.tensor(0.8)}))
+    model, cache, runner = engine_parts(d)
+    toks = tokens_for(cfg, (40,), seed=4)[0]
+    ref = plain_logits(cfg, w, toks)
+    for cuts in ((40,), (1,), (7, 2, 1)):
+        assert rel_rms(run_cut(runner, cache, "r", toks, cuts), ref) < 2e-5, cuts
+    assert rel_rms(plain_logits(cfg, {**w, "l3.mix.vmix": torch.tensor(0.0)}, toks), ref) > 1e-3
+
+
 def test_greedy_generation_through_the_entry_point(dirs):
     """Through `LLMEngine` and its scheduler: portions of prompts beside decoding requests, more requests than state
     slots, a pool that does not hold all of them at once."""

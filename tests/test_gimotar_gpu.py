@@ -440,6 +440,45 @@ def test_experts_with_a_router_bias_an_ungated_shared_expert_and_the_blocks_othe
     assert float(out[n].abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("D", [64, 200, 1030])
+def test_a_norm_whose_weight_is_stored_around_zero(dtype, D):
+    """The part adds one to the stored weight in float32; the pending term joins the stream in the same pass; selected rows."""
+    from fusezap_core_b200.parts.norm import RMSNorm
+    from fusezap_core_b200.engine.step import StepContext, Workspace
+    ops, g = cuda_ops(dtype), torch.Generator().manual_seed(D)
+    norm = RMSNorm(D, 1e-5, name="w", offset=1.0)
+    w = torch.randn(D, generator=g) * 0.3
+    norm.bind({"w": w.to(DEV)}, ops)
+    x, delta = torch.randn(9, D, generator=g), torch.randn(9, D, generator=g)
+    ctx = StepContext(ops, Workspace(torch.device(DEV), 9), Meta([(9, 0, -1)]), {}, None)
+    xd = x.to(DEV)
+    h = norm.forward(ctx, xd, delta.to(DEV))
+    close(h, plain.one_plus_norm((x + delta).to(F), w.to(F), 1e-5), dtype)
+    assert (xd.cpu() - (x + delta)).abs().max() < 1e-6
+    rows = torch.tensor([7, -1, 0], dtype=torch.int32, device=DEV)
+    h = norm.forward(ctx, xd, None, rows=rows)
+    ref = plain.one_plus_norm((x + delta)[[7, 0]].to(F), w.to(F), 1e-5)
+    close(h[[0, 2]], ref, dtype)
+    assert float(h[1].float().abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_strong_blend_of_values_shows_in_the_logits(dtype, tmp_path):
+    """Blend weights of 0.8 and -0.5 in the later layers (and a first layer's own weight that must not matter): the model
+    follows the plain one, whole, in portions and token by token, and differs from itself without the blend."""
+    def strong(t):
+        t.update({"l0.mix.vmix": torch.tensor(0.9), "l3.mix.vmix": torch.tensor(0.8)})
+    d, cfg, w = make_dir("mix", tmp_path, change=strong)
+    model, cache, runner = engine_parts(d, dtype)
+    toks = tokens_for(cfg, (60,), seed=4)[0]
+    ref = oracle(cfg, w, toks, dtype)
+    for cuts in ((60,), (1,), (7, 2, 1)):
+        agrees(run_cut(runner, cache, "r", toks, cuts), ref, dtype, cuts)
+    plainer = oracle(cfg, {**w, "l3.mix.vmix": torch.tensor(0.0)}, toks, dtype)
+    assert row_errors(plainer, ref).max() > 0.1
+
+
 # ------------------------------------------------------------------------------------------------ the model, further
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_greedy_generation_through_the_entry_point(dirs, dtype):
